@@ -1,0 +1,941 @@
+// C ABI of libcatccos_b200.so (declarations and reference citations: include/catccos_b200.h).
+// Host logic only: rank contexts, symmetric buffers (cuMem/VMM, peer mapped), epochs, launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/catccos_b200.h"
+#include "bootstrap.hpp"
+#include "common.cuh"
+#include "mx_gemm.cuh"
+#include "mx_quant.cuh"
+
+using namespace catccos;
+
+static_assert(sizeof(catccos_b200_tiling_t) == 17 * sizeof(uint32_t), "must match CocTilingParams");
+
+#define ERROR_LOG(fmt, ...) fprintf(stdout, "[ERROR] " fmt "\n", ##__VA_ARGS__)
+
+// Same shape as the reference's ACL_CHECK (utils/utils.h:28-34): print and carry the code on.
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t err__ = (expr);                                                                 \
+        if (err__ != cudaSuccess) {                                                                 \
+            fprintf(stderr, "%s:%d cudaError:%d (%s)\n", __FILE__, __LINE__, (int)err__,            \
+                    cudaGetErrorString(err__));                                                     \
+            return CATCCOS_B200_ECUDA;                                                              \
+        }                                                                                           \
+    } while (0)
+
+#define CU_TRY(expr)                                                                                \
+    do {                                                                                            \
+        CUresult err__ = (expr);                                                                    \
+        if (err__ != CUDA_SUCCESS) {                                                                \
+            fprintf(stderr, "%s:%d cudaError:%d (driver)\n", __FILE__, __LINE__, (int)err__);       \
+            return CATCCOS_B200_ECUDA;                                                              \
+        }                                                                                           \
+    } while (0)
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// driver entry points (resolved at run time so that the library links against cudart only)
+// ---------------------------------------------------------------------------------------------
+struct Driver {
+    decltype(&cuMemCreate) MemCreate = nullptr;
+    decltype(&cuMemRelease) MemRelease = nullptr;
+    decltype(&cuMemExportToShareableHandle) MemExport = nullptr;
+    decltype(&cuMemImportFromShareableHandle) MemImport = nullptr;
+    decltype(&cuMemAddressReserve) MemAddressReserve = nullptr;
+    decltype(&cuMemAddressFree) MemAddressFree = nullptr;
+    decltype(&cuMemMap) MemMap = nullptr;
+    decltype(&cuMemUnmap) MemUnmap = nullptr;
+    decltype(&cuMemSetAccess) MemSetAccess = nullptr;
+    decltype(&cuMemGetAllocationGranularity) MemGetGranularity = nullptr;
+    decltype(&cuTensorMapEncodeTiled) TensorMapEncodeTiled = nullptr;
+    bool ok = false;
+
+    template <typename F>
+    bool Get(const char* name, F& fn)
+    {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) {
+            ERROR_LOG("driver entry point %s not found", name);
+            return false;
+        }
+        fn = reinterpret_cast<F>(p);
+        return true;
+    }
+
+    bool Load()
+    {
+        if (ok) {
+            return true;
+        }
+        ok = Get("cuMemCreate", MemCreate) && Get("cuMemRelease", MemRelease) &&
+             Get("cuMemExportToShareableHandle", MemExport) && Get("cuMemImportFromShareableHandle", MemImport) &&
+             Get("cuMemAddressReserve", MemAddressReserve) && Get("cuMemAddressFree", MemAddressFree) &&
+             Get("cuMemMap", MemMap) && Get("cuMemUnmap", MemUnmap) && Get("cuMemSetAccess", MemSetAccess) &&
+             Get("cuMemGetAllocationGranularity", MemGetGranularity) &&
+             Get("cuTensorMapEncodeTiled", TensorMapEncodeTiled);
+        return ok;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// state
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kHeaderBytes = 1u << 20;       // counters + flag words at the start of a symmetric buffer
+constexpr size_t kCountersOff = 0;              // uint32 [kMaxChunks]
+constexpr uint32_t kMaxChunks = 24576;          // 16-row chunks per shard a buffer can flag
+constexpr size_t kFlagsOff = 256u << 10;        // uint32 [kMaxRanks][kMaxChunks]
+static_assert(kFlagsOff + (size_t)kMaxRanks * kMaxChunks * 4 <= kHeaderBytes, "header layout");
+static_assert(kMaxChunks * 4 <= kFlagsOff, "counter area");
+
+struct RankCtx {
+    int device = 0;
+    int num_sms = 0;
+    StatusBlock* status = nullptr;  // device memory
+    cudaStream_t side = nullptr;    // the producer kernel runs here, beside the GEMM on the caller's stream
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+struct SymmAlloc {
+    size_t size = 0;                       // bytes per rank
+    std::vector<uint8_t*> base;            // base[r]: address of rank r's copy, valid for the acting rank's device
+    std::vector<uint32_t> epoch;           // per acting rank: collectives issued on this buffer
+    std::vector<bool> released;          // local mode: which ranks have fetched their pointer
+    // VMM bookkeeping (one process per rank)
+    bool vmm = false;
+    CUdeviceptr va = 0;
+    size_t va_size = 0;
+    std::vector<CUmemGenericAllocationHandle> handles;
+};
+
+enum class Mode { kNone, kProcess, kLocal };
+
+struct State {
+    std::mutex mu;
+    Mode mode = Mode::kNone;
+    int world = 1;
+    int rank = 0;  // acting rank
+    std::vector<RankCtx> ranks;
+    std::vector<std::unique_ptr<SymmAlloc>> allocs;
+    Bootstrap boot;
+    Driver drv;
+    // options
+    int tiny_block_rule = 0;
+    int c_dtype = 0;
+    int b_layout = 0;
+    int block_n = 0;
+    int phase_mask = 3;
+    uint64_t timeout_ns = 2000ull * 1000000ull;
+    std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
+};
+
+State g;
+std::atomic<uint64_t> g_launches{0};
+
+int setup_rank_ctx(RankCtx& rc, int device)
+{
+    rc.device = device;
+    CUDA_TRY(cudaSetDevice(device));
+    CUDA_TRY(cudaFree(nullptr));
+    CUDA_TRY(cudaDeviceGetAttribute(&rc.num_sms, cudaDevAttrMultiProcessorCount, device));
+    CUDA_TRY(cudaMalloc(&rc.status, sizeof(StatusBlock)));
+    CUDA_TRY(cudaMemset(rc.status, 0, sizeof(StatusBlock)));
+    int lo = 0, hi = 0;
+    CUDA_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CUDA_TRY(cudaStreamCreateWithPriority(&rc.side, cudaStreamNonBlocking, hi));
+    CUDA_TRY(cudaEventCreateWithFlags(&rc.fork, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&rc.join, cudaEventDisableTiming));
+    return 0;
+}
+
+void destroy_rank_ctx(RankCtx& rc)
+{
+    cudaSetDevice(rc.device);
+    if (rc.status) cudaFree(rc.status);
+    if (rc.side) cudaStreamDestroy(rc.side);
+    if (rc.fork) cudaEventDestroy(rc.fork);
+    if (rc.join) cudaEventDestroy(rc.join);
+    rc = RankCtx();
+}
+
+// A world of one needs no set-up call: the first operator call adopts the current device.
+int ensure_init()
+{
+    if (g.mode != Mode::kNone) {
+        return 0;
+    }
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    g.world = 1;
+    g.rank = 0;
+    g.ranks.resize(1);
+    int rc = setup_rank_ctx(g.ranks[0], dev);
+    if (rc != 0) {
+        return rc;
+    }
+    g.mode = Mode::kProcess;
+    return 0;
+}
+
+RankCtx& cur() { return g.ranks[g.mode == Mode::kLocal ? g.rank : 0]; }
+
+SymmAlloc* find_symm(const void* p)
+{
+    for (auto& a : g.allocs) {
+        if (a && a->base[g.rank] == p) {
+            return a.get();
+        }
+    }
+    return nullptr;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct StageLayout {
+    size_t stage_bytes, codes_off, scales_off;
+};
+
+// Two stages after the header; a stage holds the gathered codes [W*M, K] then the scales [W*M, K/32].
+bool stage_layout(size_t symm_bytes, uint32_t W, uint32_t M, uint32_t K, StageLayout& L)
+{
+    if (symm_bytes < kHeaderBytes + 2048) {
+        return false;
+    }
+    L.stage_bytes = ((symm_bytes - kHeaderBytes) / 2) & ~(size_t)1023;
+    L.codes_off = 0;
+    L.scales_off = align_up((size_t)W * M * K, 1024);
+    size_t need = L.scales_off + align_up((size_t)W * M * (K / 32), 1024);
+    return need <= L.stage_bytes;
+}
+
+// ---------------------------------------------------------------------------------------------
+// launches
+// ---------------------------------------------------------------------------------------------
+int quant_grid(const RankCtx& rc, bool device_tiny, bool prequant)
+{
+    int per_sm = 0;
+    const void* fn = nullptr;
+    if (prequant) {
+        fn = (const void*)mx_quant_push_kernel<false, true>;
+    } else if (device_tiny) {
+        fn = (const void*)mx_quant_push_kernel<true, false>;
+    } else {
+        fn = (const void*)mx_quant_push_kernel<false, false>;
+    }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kQuantThreads, 0) != cudaSuccess || per_sm < 1) {
+        per_sm = 1;
+    }
+    if (per_sm > 6) {
+        per_sm = 6;
+    }
+    return per_sm * rc.num_sms;
+}
+
+void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
+{
+    const uint32_t chunks = (M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t max_segs = (K + kQuantColsPerWarpStep - 1) / kQuantColsPerWarpStep;
+    uint32_t want = ((uint32_t)num_sms * 4 + chunks - 1) / chunks;
+    if (want < 1) want = 1;
+    if (want > max_segs) want = max_segs;
+    uint32_t seg_cols = (uint32_t)align_up((K + want - 1) / want, kQuantColsPerWarpStep);
+    p.seg_cols = seg_cols;
+    p.segs_per_chunk = (K + seg_cols - 1) / seg_cols;
+}
+
+int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, bool produce)
+{
+    const bool dev_tiny = g.tiny_block_rule != 0;
+    int grid = quant_grid(rc, dev_tiny, prequant);
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    uint32_t items = produce ? chunks * p.segs_per_chunk : 0;
+    if (p.consume) {
+        uint32_t peer_items = (p.world - 1) * chunks;
+        if (peer_items > items) items = peer_items;
+    }
+    if (items == 0) {
+        return 0;
+    }
+    if ((uint32_t)grid > items) grid = (int)items;
+    p.produce = produce ? 1u : 0u;
+    if (prequant) {
+        mx_quant_push_kernel<false, true><<<grid, kQuantThreads, 0, st>>>(p);
+    } else if (dev_tiny) {
+        mx_quant_push_kernel<true, false><<<grid, kQuantThreads, 0, st>>>(p);
+    } else {
+        mx_quant_push_kernel<false, false><<<grid, kQuantThreads, 0, st>>>(p);
+    }
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                  uint32_t box_outer)
+{
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner};  // bytes (8-bit elements)
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CU_TRY(g.drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    return 0;
+}
+
+template <uint32_t BLOCK_N, bool B_MN, typename OutT>
+int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p)
+{
+    auto kern = mx_gemm_kernel<BLOCK_N, B_MN, OutT>;
+    static bool attr_done[kMaxRanks * 2] = {};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < kMaxRanks * 2 && !attr_done[dev]) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)GemmSmem<BLOCK_N>::kDynamicBytes));
+        attr_done[dev] = true;
+    }
+    kern<<<grid, kGemmThreads, GemmSmem<BLOCK_N>::kDynamicBytes, st>>>(ta, tb, p);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p)
+{
+    if (!g.drv.Load()) {
+        return CATCCOS_B200_ECUDA;
+    }
+    if (p.Mg == 0 || p.N == 0 || p.K == 0 || p.K % kGemmBlockK != 0 || p.N % 16 != 0) {
+        ERROR_LOG("mx gemm needs K %% 128 == 0 and N %% 16 == 0 (got M=%u N=%u K=%u)", p.Mg, p.N, p.K);
+        return CATCCOS_B200_EINVAL;
+    }
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)p.c) & 15u || ((uintptr_t)p.a_scales & 3u) ||
+        ((uintptr_t)p.b_scales & 1u)) {
+        ERROR_LOG("mx gemm operands must be 16-byte aligned");
+        return CATCCOS_B200_EINVAL;
+    }
+    uint32_t bn = (uint32_t)g.block_n;
+    if (bn != 128 && bn != 256) {
+        bn = (p.N % 256 == 0 || p.N > 1024) ? 256 : 128;
+    }
+    const bool b_mn = g.b_layout == 0;
+    CUtensorMap ta, tb;
+    int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM);
+    if (rcode != 0) return rcode;
+    if (b_mn) {
+        rcode = encode_map_2d(&tb, b, p.N, p.K, 128, kGemmBlockK);
+    } else {
+        rcode = encode_map_2d(&tb, b, p.K, p.N, kGemmBlockK, bn);
+    }
+    if (rcode != 0) return rcode;
+    const uint32_t tiles = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + bn - 1) / bn);
+    int grid = (int)(tiles < (uint32_t)rc.num_sms ? tiles : (uint32_t)rc.num_sms);
+    p.status = rc.status;
+    p.timeout_ns = g.timeout_ns;
+    const bool f16 = g.c_dtype == 1;
+#define CATCCOS_GEMM_CASE(BN, MN)                                                             \
+    if (bn == BN && b_mn == MN) {                                                             \
+        return f16 ? launch_gemm_inst<BN, MN, __half>(grid, st, ta, tb, p)                    \
+                   : launch_gemm_inst<BN, MN, __nv_bfloat16>(grid, st, ta, tb, p);            \
+    }
+    CATCCOS_GEMM_CASE(256, true)
+    CATCCOS_GEMM_CASE(256, false)
+    CATCCOS_GEMM_CASE(128, true)
+    CATCCOS_GEMM_CASE(128, false)
+#undef CATCCOS_GEMM_CASE
+    return CATCCOS_B200_EINVAL;
+}
+
+__global__ void transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
+                                    uint32_t cols)
+{
+    __shared__ uint8_t tile[64][65];
+    const uint32_t c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+    for (uint32_t i = threadIdx.y; i < 64; i += blockDim.y) {
+        uint32_t r = r0 + i, c = c0 + threadIdx.x;
+        tile[i][threadIdx.x] = (r < rows && c < cols) ? in[(size_t)r * cols + c] : 0;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.y; i < 64; i += blockDim.y) {
+        uint32_t c = c0 + i, r = r0 + threadIdx.x;
+        if (c < cols && r < rows) {
+            out[(size_t)c * rows + r] = tile[threadIdx.x][i];
+        }
+    }
+}
+
+// Common part of the two AllGather-Matmul entry points.
+int allgather_matmul(void* stream, const void* a, const void* a_scale, bool prequant, const void* b,
+                     const void* b_scale, void* c, void* symm, const catccos_b200_tiling_t* t)
+{
+    if (!t || !a || !b || !b_scale || !c || (prequant && !a_scale)) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    const uint32_t M = t->m, K = t->k, N = t->n, W = t->rankSize;
+    if (W != (uint32_t)g.world || M == 0 || K % kGemmBlockK != 0 || N % 16 != 0) {
+        ERROR_LOG("allgather matmul: rankSize %u (world %d), M=%u K=%u N=%u unsupported", W, g.world, M, K, N);
+        return CATCCOS_B200_EINVAL;
+    }
+    SymmAlloc* sa = find_symm(symm);
+    if (sa == nullptr) {
+        ERROR_LOG("allgather matmul: symm must come from catccos_b200_symm_alloc");
+        return CATCCOS_B200_ENOTSYMM;
+    }
+    StageLayout L;
+    const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
+    if (!stage_layout(sa->size, W, M, K, L) || chunks > kMaxChunks) {
+        ERROR_LOG("allgather matmul: symmetric buffer of %zu bytes too small", sa->size);
+        return CATCCOS_B200_ENOMEM;
+    }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool produce = (g.phase_mask & 1) != 0, consume = (g.phase_mask & 2) != 0;
+    if (produce) {
+        sa->epoch[g.rank] += 1;
+    }
+    const uint32_t epoch = sa->epoch[g.rank];
+    const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * L.stage_bytes;
+    const uint32_t rank = (uint32_t)g.rank;
+
+    if (produce) {
+        QuantPushParams q = {};
+        q.in = a;
+        q.in_scales = (const uint8_t*)a_scale;
+        q.M = M;
+        q.K = K;
+        q.rank = rank;
+        q.world = W;
+        q.epoch = epoch;
+        q.num_dst = W;
+        q.publish = 1;
+        choose_segments(M, K, rc.num_sms, q);
+        for (uint32_t d = 0; d < W; ++d) {
+            uint8_t* base = sa->base[d] + stage_off;
+            q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
+            q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
+            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxChunks;
+        }
+        q.counters = reinterpret_cast<uint32_t*>(sa->base[rank] + kCountersOff);
+        q.status = rc.status;
+        q.timeout_ns = g.timeout_ns;
+        cudaStream_t qs = consume ? rc.side : st;
+        if (consume) {
+            CUDA_TRY(cudaEventRecord(rc.fork, st));
+            CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
+        }
+        rcode = launch_quant_push(rc, qs, q, prequant, true);
+        if (rcode != 0) return rcode;
+        if (consume) {
+            CUDA_TRY(cudaEventRecord(rc.join, rc.side));
+        }
+    }
+    if (consume) {
+        GemmParams p = {};
+        uint8_t* base = sa->base[rank] + stage_off;
+        p.a_scales = base + L.scales_off;
+        p.b_scales = (const uint8_t*)b_scale;
+        p.c = c;
+        p.Mg = W * M;
+        p.N = N;
+        p.K = K;
+        p.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
+        p.flag_stride = kMaxChunks;
+        p.world = W;
+        p.rank = rank;
+        p.m_local = M;
+        p.epoch = epoch;
+        rcode = launch_gemm(rc, st, base + L.codes_off, b, p);
+        if (rcode != 0) return rcode;
+        if (produce) {
+            CUDA_TRY(cudaStreamWaitEvent(st, rc.join, 0));
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+int catccos_b200_init(int rank, int world, int device, const char* ip_port)
+{
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (g.mode != Mode::kNone) {
+        ERROR_LOG("catccos_b200_init: already initialised");
+        return CATCCOS_B200_ESTATE;
+    }
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) {
+        ERROR_LOG("catccos_b200_init: rank %d of %d unsupported (at most %d ranks)", rank, world, kMaxRanks);
+        return CATCCOS_B200_EINVAL;
+    }
+    g.world = world;
+    g.rank = rank;
+    g.ranks.resize(1);
+    int rc = setup_rank_ctx(g.ranks[0], device);
+    if (rc != 0) return rc;
+    if (world > 1) {
+        if (!g.drv.Load()) return CATCCOS_B200_ECUDA;
+        if (!g.boot.Init(rank, world, ip_port)) {
+            ERROR_LOG("catccos_b200_init: rendezvous failed: %s", g.boot.error().c_str());
+            return CATCCOS_B200_ENET;
+        }
+    }
+    g.mode = Mode::kProcess;
+    return 0;
+}
+
+int catccos_b200_init_local(int world, const int* devices)
+{
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (g.mode != Mode::kNone) {
+        ERROR_LOG("catccos_b200_init_local: already initialised");
+        return CATCCOS_B200_ESTATE;
+    }
+    if (world < 1 || world > kMaxRanks || devices == nullptr) {
+        return CATCCOS_B200_EINVAL;
+    }
+    g.world = world;
+    g.rank = 0;
+    g.ranks.resize(world);
+    g.local_alloc_cursor.assign(world, 0);
+    for (int r = 0; r < world; ++r) {
+        int rc = setup_rank_ctx(g.ranks[r], devices[r]);
+        if (rc != 0) return rc;
+    }
+    // ranks on different GPUs reach one another's memory through peer access
+    for (int r = 0; r < world; ++r) {
+        for (int s = 0; s < world; ++s) {
+            if (devices[r] != devices[s]) {
+                cudaSetDevice(devices[r]);
+                cudaError_t e = cudaDeviceEnablePeerAccess(devices[s], 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+                    fprintf(stderr, "%s:%d cudaError:%d (peer access %d->%d)\n", __FILE__, __LINE__, (int)e, devices[r],
+                            devices[s]);
+                    return CATCCOS_B200_ECUDA;
+                }
+                cudaGetLastError();
+            }
+        }
+    }
+    g.mode = Mode::kLocal;
+    return 0;
+}
+
+int catccos_b200_set_rank(int rank)
+{
+    if (g.mode != Mode::kLocal || rank < 0 || rank >= g.world) {
+        return CATCCOS_B200_ESTATE;
+    }
+    g.rank = rank;
+    CUDA_TRY(cudaSetDevice(g.ranks[rank].device));
+    return 0;
+}
+
+int catccos_b200_finalize(void)
+{
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (g.mode == Mode::kNone) {
+        return 0;
+    }
+    for (auto& rc : g.ranks) {
+        cudaSetDevice(rc.device);
+        cudaDeviceSynchronize();
+    }
+    for (auto& a : g.allocs) {
+        if (!a) continue;
+        if (a->vmm) {
+            g.drv.MemUnmap(a->va, a->va_size);
+            for (auto h : a->handles) g.drv.MemRelease(h);
+            g.drv.MemAddressFree(a->va, a->va_size);
+        } else if (g.mode == Mode::kLocal) {
+            for (int r = 0; r < g.world; ++r) {
+                cudaSetDevice(g.ranks[r].device);
+                cudaFree(a->base[r]);
+            }
+        } else {
+            cudaFree(a->base[0]);
+        }
+    }
+    g.allocs.clear();
+    for (auto& rc : g.ranks) destroy_rank_ctx(rc);
+    g.ranks.clear();
+    g.boot.Close();
+    g.mode = Mode::kNone;
+    g.world = 1;
+    g.rank = 0;
+    return 0;
+}
+
+int catccos_b200_symm_alloc(size_t bytes, void** local_ptr)
+{
+    if (local_ptr == nullptr || bytes == 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    std::lock_guard<std::mutex> lock(g.mu);
+    const int W = g.world;
+    if (g.mode == Mode::kLocal) {
+        // the k-th call of every rank names the same allocation
+        uint32_t idx = g.local_alloc_cursor[g.rank]++;
+        uint32_t seen = 0;
+        SymmAlloc* sa = nullptr;
+        for (auto& a : g.allocs) {
+            if (a && seen++ == idx) {
+                sa = a.get();
+                break;
+            }
+        }
+        if (sa == nullptr) {
+            auto na = std::make_unique<SymmAlloc>();
+            na->size = align_up(bytes, 1024);
+            na->base.assign(W, nullptr);
+            na->epoch.assign(W, 0);
+            na->released.assign(W, false);
+            for (int r = 0; r < W; ++r) {
+                CUDA_TRY(cudaSetDevice(g.ranks[r].device));
+                CUDA_TRY(cudaMalloc(&na->base[r], na->size));
+                CUDA_TRY(cudaMemset(na->base[r], 0, na->size));
+            }
+            for (int r = 0; r < W; ++r) {
+                CUDA_TRY(cudaSetDevice(g.ranks[r].device));
+                CUDA_TRY(cudaDeviceSynchronize());
+            }
+            CUDA_TRY(cudaSetDevice(g.ranks[g.rank].device));
+            sa = na.get();
+            g.allocs.push_back(std::move(na));
+        } else if (sa->size < bytes) {
+            ERROR_LOG("symm_alloc: ranks disagree on the size of allocation %u", idx);
+            return CATCCOS_B200_EINVAL;
+        }
+        *local_ptr = sa->base[g.rank];
+        return 0;
+    }
+    RankCtx& rc = g.ranks[0];
+    CUDA_TRY(cudaSetDevice(rc.device));
+    auto na = std::make_unique<SymmAlloc>();
+    na->base.assign(W, nullptr);
+    na->epoch.assign(W, 0);
+    if (W == 1) {
+        na->size = align_up(bytes, 1024);
+        CUDA_TRY(cudaMalloc(&na->base[0], na->size));
+        CUDA_TRY(cudaMemset(na->base[0], 0, na->size));
+        CUDA_TRY(cudaDeviceSynchronize());
+    } else {
+        Driver& d = g.drv;
+        CUmemAllocationProp prop = {};
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = rc.device;
+        prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        size_t gran = 0;
+        CU_TRY(d.MemGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+        na->size = align_up(bytes, gran);
+        na->vmm = true;
+        na->handles.assign(W, 0);
+        CU_TRY(d.MemCreate(&na->handles[g.rank], na->size, &prop, 0));
+        int my_fd = -1;
+        CU_TRY(d.MemExport(&my_fd, na->handles[g.rank], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+        std::vector<int> fds;
+        if (!g.boot.ExchangeFds(my_fd, fds)) {
+            ERROR_LOG("symm_alloc: handle exchange failed: %s", g.boot.error().c_str());
+            return CATCCOS_B200_ENET;
+        }
+        for (int r = 0; r < W; ++r) {
+            if (r != g.rank) {
+                CU_TRY(d.MemImport(&na->handles[r], (void*)(uintptr_t)fds[r], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+            }
+            close(fds[r]);
+        }
+        na->va_size = na->size * W;
+        CU_TRY(d.MemAddressReserve(&na->va, na->va_size, gran, 0, 0));
+        CUmemAccessDesc acc = {};
+        acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        acc.location.id = rc.device;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        for (int r = 0; r < W; ++r) {
+            CU_TRY(d.MemMap(na->va + (size_t)r * na->size, na->size, 0, na->handles[r], 0));
+            na->base[r] = reinterpret_cast<uint8_t*>(na->va + (size_t)r * na->size);
+        }
+        CU_TRY(d.MemSetAccess(na->va, na->va_size, &acc, 1));
+        CUDA_TRY(cudaMemset(na->base[g.rank], 0, na->size));
+        CUDA_TRY(cudaDeviceSynchronize());
+        if (!g.boot.Barrier()) {  // nobody pushes into a buffer that is still being cleared
+            return CATCCOS_B200_ENET;
+        }
+    }
+    *local_ptr = na->base[g.rank];
+    g.allocs.push_back(std::move(na));
+    return 0;
+}
+
+int catccos_b200_symm_free(void* local_ptr)
+{
+    std::lock_guard<std::mutex> lock(g.mu);
+    for (auto& a : g.allocs) {
+        if (!a || a->base[g.rank] != local_ptr) {
+            continue;
+        }
+        if (g.mode == Mode::kLocal) {
+            a->released[g.rank] = true;  // freed once every rank has let go
+            bool all = true;
+            for (int r = 0; r < g.world; ++r) all = all && a->released[r];
+            if (!all) return 0;
+            for (int r = 0; r < g.world; ++r) {
+                cudaSetDevice(g.ranks[r].device);
+                cudaDeviceSynchronize();
+                cudaFree(a->base[r]);
+            }
+            cudaSetDevice(g.ranks[g.rank].device);
+        } else {
+            CUDA_TRY(cudaDeviceSynchronize());
+            if (a->vmm) {
+                g.boot.Barrier();  // peers may still be storing into this rank's copy
+                g.drv.MemUnmap(a->va, a->va_size);
+                for (auto h : a->handles) g.drv.MemRelease(h);
+                g.drv.MemAddressFree(a->va, a->va_size);
+            } else {
+                cudaFree(a->base[0]);
+            }
+        }
+        a.reset();
+        return 0;
+    }
+    return CATCCOS_B200_ENOTSYMM;
+}
+
+size_t catccos_b200_symm_bytes_needed(const catccos_b200_tiling_t* t, int quant_op)
+{
+    if (t == nullptr) return 0;
+    const size_t W = t->rankSize ? t->rankSize : 1;
+    const size_t M = t->m;
+    const size_t K = quant_op ? t->n : t->k;
+    return kHeaderBytes + 2 * (align_up(W * M * K, 1024) + align_up(W * M * (K / 32), 1024)) + 2048;
+}
+
+int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint32_t k, void* codes, void* scales)
+{
+    if (!in_bf16 || !codes || !scales || rows == 0 || k == 0 || k % 32 != 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    if (((uintptr_t)in_bf16 | (uintptr_t)codes) & 15u) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    RankCtx& rc = cur();
+    QuantPushParams q = {};
+    q.in = in_bf16;
+    q.M = rows;
+    q.K = k;
+    q.world = 1;
+    q.num_dst = 1;
+    q.dst_codes[0] = (uint8_t*)codes;
+    q.dst_scales[0] = (uint8_t*)scales;
+    choose_segments(rows, k, rc.num_sms, q);
+    q.publish = 0;
+    q.status = rc.status;
+    q.timeout_ns = g.timeout_ns;
+    return launch_quant_push(rc, (cudaStream_t)stream, q, false, true);
+}
+
+int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out_codes, void* out_scales, void* symm,
+                                    const catccos_b200_tiling_t* t, uint32_t magic)
+{
+    (void)magic;
+    if (!t || !in_bf16 || !out_codes || !out_scales) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    const uint32_t M = t->m, K = t->n, W = t->rankSize;  // the quantised axis is called n here
+    if (W != (uint32_t)g.world || M == 0 || K == 0 || K % 32 != 0) {
+        ERROR_LOG("mx quant allgather: rankSize %u (world %d), M=%u N=%u: N must be a positive multiple of 32", W,
+                  g.world, M, K);
+        return CATCCOS_B200_EINVAL;
+    }
+    if (((uintptr_t)in_bf16 | (uintptr_t)out_codes) & 15u) {
+        return CATCCOS_B200_EINVAL;
+    }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    const uint32_t rank = (uint32_t)g.rank;
+    QuantPushParams q = {};
+    q.in = in_bf16;
+    q.M = M;
+    q.K = K;
+    q.rank = rank;
+    q.world = W;
+    q.num_dst = W;
+    q.status = rc.status;
+    q.timeout_ns = g.timeout_ns;
+    choose_segments(M, K, rc.num_sms, q);
+    uint8_t* oc = (uint8_t*)out_codes;
+    uint8_t* os = (uint8_t*)out_scales;
+    if (W == 1) {
+        q.dst_codes[0] = oc;
+        q.dst_scales[0] = os;
+        return launch_quant_push(rc, (cudaStream_t)stream, q, false, true);
+    }
+    SymmAlloc* sa = find_symm(symm);
+    if (sa == nullptr) {
+        ERROR_LOG("mx quant allgather: symm must come from catccos_b200_symm_alloc");
+        return CATCCOS_B200_ENOTSYMM;
+    }
+    StageLayout L;
+    const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
+    if (!stage_layout(sa->size, W, M, K, L) || chunks > kMaxChunks) {
+        ERROR_LOG("mx quant allgather: symmetric buffer of %zu bytes too small", sa->size);
+        return CATCCOS_B200_ENOMEM;
+    }
+    const bool produce = (g.phase_mask & 1) != 0, consume = (g.phase_mask & 2) != 0;
+    if (produce) {
+        sa->epoch[g.rank] += 1;
+    }
+    const uint32_t epoch = sa->epoch[g.rank];
+    const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * L.stage_bytes;
+    q.epoch = epoch;
+    q.publish = 1;
+    for (uint32_t d = 0; d < W; ++d) {
+        if (d == rank) {
+            q.dst_codes[d] = oc + (size_t)rank * M * K;
+            q.dst_scales[d] = os + (size_t)rank * M * (K / 32);
+            q.dst_flags[d] = nullptr;
+        } else {
+            uint8_t* base = sa->base[d] + stage_off;
+            q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
+            q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
+            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxChunks;
+        }
+    }
+    q.counters = reinterpret_cast<uint32_t*>(sa->base[rank] + kCountersOff);
+    q.consume = consume ? 1u : 0u;
+    q.stage_codes = sa->base[rank] + stage_off + L.codes_off;
+    q.stage_scales = sa->base[rank] + stage_off + L.scales_off;
+    q.out_codes = oc;
+    q.out_scales = os;
+    q.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
+    q.flag_stride = kMaxChunks;
+    return launch_quant_push(rc, (cudaStream_t)stream, q, false, produce);
+}
+
+int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void* b, const void* a_scale,
+                                         const void* b_scale, void* c, void* symm, const catccos_b200_tiling_t* t,
+                                         uint32_t magic)
+{
+    (void)magic;
+    return allgather_matmul(stream, a, a_scale, true, b, b_scale, c, symm, t);
+}
+
+int catccos_b200_mx_quant_allgather_matmul(void* stream, const void* a_bf16, const void* b, const void* b_scale,
+                                           void* c, void* symm, const catccos_b200_tiling_t* t, uint32_t magic)
+{
+    (void)magic;
+    return allgather_matmul(stream, a_bf16, nullptr, false, b, b_scale, c, symm, t);
+}
+
+int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,
+                         uint32_t m, uint32_t n, uint32_t k)
+{
+    if (!a || !a_scale || !b || !b_scale || !c) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    RankCtx& rc = cur();
+    GemmParams p = {};
+    p.a_scales = (const uint8_t*)a_scale;
+    p.b_scales = (const uint8_t*)b_scale;
+    p.c = c;
+    p.Mg = m;
+    p.N = n;
+    p.K = k;
+    p.flags = nullptr;
+    p.world = 1;
+    p.m_local = m;
+    return launch_gemm(rc, (cudaStream_t)stream, a, b, p);
+}
+
+int catccos_b200_transpose_weight(void* stream, const void* b, void* bt, uint32_t k, uint32_t n)
+{
+    if (!b || !bt || k == 0 || n == 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    dim3 grid((n + 63) / 64, (k + 63) / 64), block(64, 4);
+    transpose_u8_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const uint8_t*)b, (uint8_t*)bt, k, n);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int catccos_b200_last_status(uint32_t out[4])
+{
+    if (out == nullptr || g.mode == Mode::kNone) {
+        return CATCCOS_B200_ESTATE;
+    }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    StatusBlock sb;
+    CUDA_TRY(cudaMemcpy(&sb, rc.status, sizeof(sb), cudaMemcpyDeviceToHost));
+    out[0] = sb.code;
+    out[1] = sb.rank;
+    out[2] = sb.chunk;
+    out[3] = sb.epoch;
+    if (sb.code != 0) {
+        ERROR_LOG("device wait ran out: code %u rank/barrier %u chunk/stage %u epoch %u", sb.code, sb.rank, sb.chunk,
+                  sb.epoch);
+        CUDA_TRY(cudaMemset(rc.status, 0, sizeof(sb)));
+        return CATCCOS_B200_ETIMEOUT;
+    }
+    return 0;
+}
+
+int catccos_b200_set_option(const char* key, int64_t value)
+{
+    if (key == nullptr) return CATCCOS_B200_EINVAL;
+    std::string k = key;
+    if (k == "tiny_block_rule" && (value == 0 || value == 1)) {
+        g.tiny_block_rule = (int)value;
+    } else if (k == "c_dtype" && (value == 0 || value == 1)) {
+        g.c_dtype = (int)value;
+    } else if (k == "b_layout" && (value == 0 || value == 1)) {
+        g.b_layout = (int)value;
+    } else if (k == "block_n" && (value == 0 || value == 128 || value == 256)) {
+        g.block_n = (int)value;
+    } else if (k == "timeout_ms" && value > 0 && value <= 600000) {
+        g.timeout_ns = (uint64_t)value * 1000000ull;
+    } else if (k == "phase_mask" && value >= 1 && value <= 3) {
+        g.phase_mask = (int)value;
+    } else {
+        ERROR_LOG("set_option: unknown key or bad value: %s = %lld", key, (long long)value);
+        return CATCCOS_B200_EINVAL;
+    }
+    return 0;
+}
+
+uint64_t catccos_b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,299 @@
+// Shared device helpers for the sm_100a kernels: status words, bounded waits, mbarrier / TMA /
+// tcgen05 PTX wrappers.  Every spin in this library goes through a bounded wait: when the limit
+// runs out the waiter records what it was waiting for in the status block and carries on, so a
+// kernel always runs to its end (and frees its tensor memory) even when a peer never shows up.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace catccos {
+
+constexpr int kMaxRanks = 8;  // one NVSwitch box; the reference scripts cap ranks per host at 8 too
+
+// Error codes written to StatusBlock::code (0 = ok).  The host reads them after the stream
+// has been synchronised; the C ABI returns them from catccos_b200_last_status.
+enum StatusCode : uint32_t {
+    kStatusOk = 0,
+    kStatusFlagTimeout = 1,      // a (source rank, chunk) ready flag did not arrive in time
+    kStatusBarrierTimeout = 2,   // an intra-kernel mbarrier wait ran out (a bug, never a peer)
+    kStatusHandshakeTimeout = 3, // a peer did not enter the collective in time
+};
+
+struct StatusBlock {
+    uint32_t code;   // first error wins
+    uint32_t rank;   // the rank waited for (or the barrier id)
+    uint32_t chunk;  // the chunk waited for (or stage index)
+    uint32_t epoch;  // the epoch the waiter expected
+};
+
+__device__ __forceinline__ void report_status(StatusBlock* st, uint32_t code, uint32_t rank, uint32_t chunk,
+                                              uint32_t epoch)
+{
+    if (st != nullptr && atomicCAS(&st->code, 0u, code) == 0u) {
+        st->rank = rank;
+        st->chunk = chunk;
+        st->epoch = epoch;
+        __threadfence_system();
+    }
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits until *flag >= want (epochs only grow).  Returns false when timeout_ns ran out.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t timeout_ns)
+{
+    if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) {
+        return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) {
+            return true;
+        }
+        if ((++spins & 0x3Fu) == 0u) {
+            if (globaltimer_ns() - t0 > timeout_ns) {
+                return false;
+            }
+            __nanosleep(64);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// shared memory / mbarrier
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded mbarrier wait.  The limit (about two seconds of polling) is far beyond any legitimate
+// wait inside one kernel; if it runs out the kernel records a status and continues with whatever
+// is in shared memory, which keeps the grid from hanging on a protocol bug.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id, uint32_t stage)
+{
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xFFu) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
+            report_status(st, kStatusBarrierTimeout, id, stage, parity);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void fence_proxy_async_shared()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_all()
+{
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA (tiled bulk tensor copies, this GPU's memory only, never cluster multicast)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------
+// tcgen05: tensor memory, UMMA descriptors, MMA issue
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Makes the mbarrier track completion of all tcgen05 operations issued so far by this thread.
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
+// (each >> 4), descriptor version 1 at bit 46, swizzle mode in bits 61..63
+// (0 none, 2 = 128-byte swizzle, 4 = 64-byte, 6 = 32-byte).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(layout_type & 7u) << 61;
+    return d;
+}
+
+// Instruction descriptor for tcgen05.mma.kind::mxf8f6f4.block_scale with E4M3 x E4M3 operands,
+// UE8M0 scale factors and fp32 accumulation.
+//   bits  4..5  B scale-factor id (which byte of the 32-bit scale word)
+//   bits  7..9  A format (0 = E4M3)      bits 10..12 B format (0 = E4M3)
+//   bit  15     A major (0 = K)          bit  16     B major (0 = K, 1 = MN)
+//   bits 17..22 N >> 3                   bit  23     scale format (1 = UE8M0)
+//   bits 24..28 M >> 4                   bits 29..30 A scale-factor id
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t M, uint32_t N, bool b_mn_major)
+{
+    return (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) | ((N >> 3) << 17) | (1u << 23) |
+           ((M >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t idesc_with_sf_id(uint32_t idesc, uint32_t sf_id)
+{
+    return idesc | (sf_id << 4) | (sf_id << 29);
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// Copies one 512-byte scale-factor atom (32 rows x 16 bytes) from shared memory into four
+// tensor-memory columns, replicated over the four 32-lane groups.
+__device__ __forceinline__ void tcgen05_cp_sf(uint32_t tmem_dst, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (lane = TMEM lane).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+}  // namespace catccos

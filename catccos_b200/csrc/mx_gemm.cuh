@@ -1,0 +1,421 @@
+// MXFP8 block-scaled GEMM for sm_100a: C[Mg, N] = dequant(A)[Mg, K] x dequant(B)[K, N].
+//
+// It replaces the cube-core half of the reference's AllGather-Matmul kernel
+// (include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:240-297; its main loop is CATLASS
+// BlockMmadTla<MmadMx>, instantiated in
+// examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_device.h:47-57).
+//
+//   A      E4M3 codes, row-major [Mg, K]   (K-major operand; Mg = world * M_local gathered rows)
+//   SFA    E8M0 bytes, row-major [Mg, K/32]
+//   B      E4M3 codes, row-major [K, N]    (MN-major operand, read in place)   -- or --
+//          the transposed copy [N, K]      (K-major operand, made once by the weight-prepare kernel)
+//   SFB    E8M0 bytes in the reference's file layout [K/64, N, 2]
+//   C      bf16 or fp16, row-major [Mg, N]
+//
+// One CTA per 128 x BLOCK_N output tile, persistent over tiles, 256 threads:
+//   warp 0    TMA producer: A and B tiles (128-byte swizzle) into a ring of shared-memory stages
+//   warp 1    MMA issuer: tcgen05.cp of the scale atoms into tensor memory, then four
+//             tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per stage
+//   warps 2-3 scale loaders: plain global loads of the E8M0 bytes, written to shared memory in
+//             the 32x16-byte atom layout tcgen05.cp expects
+//   warps 4-7 epilogue: tcgen05.ld of the fp32 accumulator, convert, 16-byte global stores
+//
+// When `flags` is set, a tile is not touched before every (source rank, 16-row chunk) under its
+// rows has been published with the current epoch by the quantise-and-push kernel; tiles are
+// visited in the order the chunks arrive (own shard first, then chunk by chunk over the peers).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace catccos {
+
+constexpr uint32_t kGemmBlockM = 128;
+constexpr uint32_t kGemmBlockK = 128;   // bytes == elements (8-bit codes): one 128-byte swizzle row
+constexpr uint32_t kGemmThreads = 256;
+constexpr uint32_t kRowsPerChunk = 16;  // granularity of the ready flags
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+    const uint8_t* a_scales;  // [Mg, K/32]
+    const uint8_t* b_scales;  // [K/64, N, 2]
+    void* c;                  // [Mg, N]
+    uint32_t Mg, N, K;
+    // gating on the quantise-and-push kernel (flags == nullptr: all of A is already in place)
+    const uint32_t* flags;  // [world][flag_stride] epoch words in this GPU's symmetric header
+    uint32_t flag_stride;
+    uint32_t world, rank, m_local, epoch;
+    uint64_t timeout_ns;
+    StatusBlock* status;
+};
+
+template <uint32_t BLOCK_N>
+struct GemmSmem {
+    static constexpr uint32_t kStages = (BLOCK_N == 256) ? 4 : 6;
+    static constexpr uint32_t kABytes = kGemmBlockM * kGemmBlockK;
+    static constexpr uint32_t kBBytes = BLOCK_N * kGemmBlockK;
+    static constexpr uint32_t kSfaBytes = 512;
+    static constexpr uint32_t kSfbAtoms = (BLOCK_N + 127) / 128;
+    static constexpr uint32_t kSfbBytes = kSfbAtoms * 512;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kOffA + kStages * kABytes;
+    static constexpr uint32_t kOffSfa = kOffB + kStages * kBBytes;
+    static constexpr uint32_t kOffSfb = kOffSfa + kStages * kSfaBytes;
+    static constexpr uint32_t kOffBar = kOffSfb + kStages * kSfbBytes;
+    // barriers: full_ab[S], full_sf[S], empty[S], tmem_full[2], tmem_empty[2], overlap_free[2]
+    static constexpr uint32_t kNumBars = 3 * kStages + 6;
+    static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr uint32_t kBytes = kOffTmemPtr + 16;
+    static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack to align the base to 1024 bytes
+    // accumulator placement in tensor memory: two 128 x BLOCK_N fp32 accumulators.  For
+    // BLOCK_N = 256 they overlap by 16 columns (240..255) so that 16 columns stay free for the
+    // scale factors; the epilogue drains the shared columns first and then lets the next tile start.
+    static constexpr bool kOverlap = (BLOCK_N == 256);
+    static constexpr uint32_t kAccCol1 = kOverlap ? 240 : 256;
+    static constexpr uint32_t kSfCol = kOverlap ? 496 : 480;  // SFA: 4 columns, SFB: 4 per 128 columns of N
+};
+
+struct TileCoord {
+    uint32_t m_tile, n_tile;
+};
+
+// Tile visiting order.  n runs fastest so that concurrently running CTAs share one A panel in L2.
+// With gating, m tiles follow arrival: this rank's own shard first, then for each 128-row slice of
+// a shard, the peers in ring order starting after this rank.
+__device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
+{
+    uint32_t mo = idx / n_tiles;
+    TileCoord t;
+    t.n_tile = idx - mo * n_tiles;
+    if (p.flags != nullptr && p.world > 1) {
+        if (p.m_local % kGemmBlockM == 0) {
+            uint32_t tps = p.m_local / kGemmBlockM;
+            if (mo < tps) {
+                t.m_tile = p.rank * tps + mo;
+            } else {
+                uint32_t j = mo - tps;
+                uint32_t mt = j / (p.world - 1);
+                uint32_t src = (p.rank + 1 + j % (p.world - 1)) % p.world;
+                t.m_tile = src * tps + mt;
+            }
+        } else {
+            uint32_t first = (p.rank * p.m_local) / kGemmBlockM;
+            t.m_tile = (mo + first) % m_tiles;
+        }
+    } else {
+        t.m_tile = mo;
+    }
+    return t;
+}
+
+// Waits (whole warp) until every chunk under gathered rows [m0, m0 + 128) carries the epoch.
+__device__ __forceinline__ void wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane)
+{
+    uint32_t prev_src = 0xFFFFFFFFu, prev_chunk = 0xFFFFFFFFu;
+    for (uint32_t i = 0; i < 4; ++i) {
+        uint32_t row = m0 + lane * 4 + i;
+        if (row >= p.Mg) {
+            break;
+        }
+        uint32_t src = row / p.m_local;
+        uint32_t chunk = (row - src * p.m_local) / kRowsPerChunk;
+        if (src == prev_src && chunk == prev_chunk) {
+            continue;
+        }
+        prev_src = src;
+        prev_chunk = chunk;
+        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk, p.epoch, p.timeout_ns)) {
+            report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
+        }
+    }
+    __syncwarp();
+}
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b)
+{
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <uint32_t BLOCK_N, bool B_MN_MAJOR, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
+{
+    using S = GemmSmem<BLOCK_N>;
+    constexpr uint32_t kStages = S::kStages;
+    static_assert(BLOCK_N == 128 || BLOCK_N == 256, "tile widths wired up: 128 and 256");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kOffBar);
+    uint64_t* full_ab = bars;
+    uint64_t* full_sf = bars + kStages;
+    uint64_t* empty = bars + 2 * kStages;
+    uint64_t* tmem_full = bars + 3 * kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint64_t* overlap_free = tmem_empty + 2;
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    const uint32_t m_tiles = (p.Mg + kGemmBlockM - 1) / kGemmBlockM;
+    const uint32_t n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+    const uint32_t num_tiles = m_tiles * n_tiles;
+    const uint32_t k_tiles = p.K / kGemmBlockK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(&full_ab[s], 1);
+            mbar_init(&full_sf[s], 2);
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 4);
+            mbar_init(&overlap_free[a], 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr_smem, kTmemCols);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------------
+        uint32_t it = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kGemmBlockM;
+            const uint32_t n0 = tc.n_tile * BLOCK_N;
+            if (p.flags != nullptr) {
+                wait_rows_ready(p, m0, lane);
+                fence_proxy_async_all();
+            }
+            if (lane == 0) {
+                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    mbar_wait(&empty[s], ph ^ 1u, p.status, 100, s);
+                    mbar_arrive_expect_tx(&full_ab[s], S::kABytes + S::kBBytes);
+                    tma_load_2d(smem + S::kOffA + s * S::kABytes, &tmap_a, &full_ab[s], (int32_t)(kt * kGemmBlockK),
+                                (int32_t)m0);
+                    if constexpr (B_MN_MAJOR) {
+                        // [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
+                        for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
+                            tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full_ab[s],
+                                        (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
+                        }
+                    } else {
+                        // transposed copy [N, K]: box = 128 (K, contiguous) x BLOCK_N rows
+                        tma_load_2d(smem + S::kOffB + s * S::kBBytes, &tmap_b, &full_ab[s],
+                                    (int32_t)(kt * kGemmBlockK), (int32_t)n0);
+                    }
+                }
+            } else {
+                it += k_tiles;
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR);
+            const uint32_t sfa_col = tmem_base + S::kSfCol;
+            const uint32_t sfb_col = tmem_base + S::kSfCol + 4;
+            uint32_t it = 0;
+            uint32_t ti = 0;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
+                const uint32_t acc = ti & 1u;
+                const uint32_t acc_ph = (ti >> 1) & 1u;
+                const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
+                mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, p.status, 101, acc);
+                if (S::kOverlap && ti > 0) {
+                    mbar_wait(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 102, acc);
+                }
+                tcgen05_fence_after();
+                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    mbar_wait(&full_sf[s], ph, p.status, 103, s);
+                    mbar_wait(&full_ab[s], ph, p.status, 104, s);
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + S::kOffA + s * S::kABytes);
+                    const uint32_t b_addr = smem_u32(smem + S::kOffB + s * S::kBBytes);
+                    // scale atoms -> tensor memory (32 rows x 16 bytes each, no swizzle, 8-row groups 128 bytes apart)
+                    tcgen05_cp_sf(sfa_col, make_smem_desc(smem_u32(smem + S::kOffSfa + s * S::kSfaBytes), 0, 128, 0));
+                    for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
+                        tcgen05_cp_sf(sfb_col + 4 * h,
+                                      make_smem_desc(smem_u32(smem + S::kOffSfb + s * S::kSfbBytes + h * 512u), 0, 128, 0));
+                    }
+#pragma unroll
+                    for (uint32_t kb = 0; kb < kGemmBlockK / 32; ++kb) {
+                        // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; K advances 32 bytes in the row
+                        const uint64_t da = make_smem_desc(a_addr + kb * 32u, 16, 1024, 2);
+                        uint64_t db;
+                        if constexpr (B_MN_MAJOR) {
+                            // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart,
+                            // 8-row K groups 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO)
+                            db = make_smem_desc(b_addr + kb * 4096u, 16384, 1024, 2);
+                        } else {
+                            db = make_smem_desc(b_addr + kb * 32u, 16, 1024, 2);
+                        }
+                        umma_mxf8(d_col, da, db, idesc_with_sf_id(idesc, kb), sfa_col, sfb_col, (kt | kb) != 0u);
+                    }
+                    tcgen05_commit(&empty[s]);
+                }
+                tcgen05_commit(&tmem_full[acc]);
+            }
+        }
+        __syncwarp();
+    } else if (warp < 4) {
+        // ------------------------------- scale loaders ------------------------------------
+        const uint32_t t = threadIdx.x - 64;  // 0..63
+        const uint32_t sf_row_bytes = p.K / 32;
+        uint32_t it = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kGemmBlockM;
+            const uint32_t n0 = tc.n_tile * BLOCK_N;
+            if (p.flags != nullptr) {
+                wait_rows_ready(p, m0, lane);
+            }
+            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1u;
+                // issue the global loads before waiting for the stage to drain
+                uint32_t va[2], vb[BLOCK_N / 64];
+#pragma unroll
+                for (uint32_t i = 0; i < 2; ++i) {
+                    const uint32_t row = m0 + t + i * 64;
+                    va[i] = 0x7F7F7F7Fu;
+                    if (row < p.Mg) {
+                        va[i] = __ldcg(reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u));
+                    }
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < BLOCK_N / 64; ++i) {
+                    const uint32_t n = n0 + t + i * 64;
+                    vb[i] = 0x7F7F7F7Fu;
+                    if (n < p.N) {
+                        const uint16_t lo =
+                            __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt) * p.N + n) * 2));
+                        const uint16_t hi =
+                            __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt + 1) * p.N + n) * 2));
+                        vb[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+                    }
+                }
+                mbar_wait(&empty[s], ph ^ 1u, p.status, 105, s);
+                uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
+                uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
+#pragma unroll
+                for (uint32_t i = 0; i < 2; ++i) {
+                    const uint32_t r = t + i * 64;
+                    *reinterpret_cast<uint32_t*>(sfa + (r & 31u) * 16u + (r >> 5) * 4u) = va[i];
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < BLOCK_N / 64; ++i) {
+                    const uint32_t n = t + i * 64;
+                    *reinterpret_cast<uint32_t*>(sfb + (n >> 7) * 512u + (n & 31u) * 16u + ((n & 127u) >> 5) * 4u) = vb[i];
+                }
+                fence_proxy_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full_sf[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------- epilogue -----------------------------------------
+        const uint32_t q = warp - 4;  // TMEM lane quarter == warp index modulo 4
+        OutT* c = reinterpret_cast<OutT*>(p.c);
+        constexpr uint32_t kChunks = BLOCK_N / 32;
+        uint32_t ti = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
+            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kGemmBlockM;
+            const uint32_t n0 = tc.n_tile * BLOCK_N;
+            const uint32_t acc = ti & 1u;
+            const uint32_t acc_ph = (ti >> 1) & 1u;
+            const uint32_t d_col = acc ? S::kAccCol1 : 0u;
+            mbar_wait(&tmem_full[acc], acc_ph, p.status, 106, acc);
+            tcgen05_fence_after();
+            const uint32_t row = m0 + q * 32 + lane;
+            // the chunk that holds the columns shared with the other accumulator goes first
+            const uint32_t first = (S::kOverlap && acc == 0) ? (kChunks - 1) : 0u;
+            for (uint32_t ci = 0; ci < kChunks; ++ci) {
+                uint32_t chunk = ci;
+                if (S::kOverlap && acc == 0) {
+                    chunk = (ci == 0) ? first : ci - 1;
+                }
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + d_col + chunk * 32u, r);
+                tmem_ld_wait();
+                if (S::kOverlap && ci == 0) {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&overlap_free[acc]);
+                    }
+                }
+                const uint32_t col = n0 + chunk * 32u;
+                if (row < p.Mg && col < p.N) {
+                    OutT* dst = c + (size_t)row * p.N + col;
+                    if (col + 32u <= p.N) {
+#pragma unroll
+                        for (uint32_t v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2<OutT>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                            o.y = pack2<OutT>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                            o.z = pack2<OutT>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                            o.w = pack2<OutT>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                            *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t j = 0; j < 32u; ++j) {
+                            if (col + j < p.N) {
+                                dst[j] = static_cast<OutT>(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&tmem_empty[acc]);
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace catccos

@@ -1,0 +1,268 @@
+// MX quantise-and-push kernel for sm_100a: bf16 [M, K] -> E4M3 codes + one E8M0 scale per 32
+// K-elements, stored straight into every destination rank's buffer (peer-mapped over NVLink), with a
+// ready flag per (source rank, 16-row chunk).
+//
+// It replaces the vector-core program of the reference:
+//   arithmetic   include/catccos/comm/block/comm_block_mx_quant.hpp:413-523,569-664 (ComputeMxQuant, FP8)
+//   streaming    include/catccos/comm/block/comm_block_mx_quant.hpp:155-207 (operator())
+//   allgather    include/catccos/comm/kernel/mx_quant_allgather.hpp:132-287 (quantise into the symmetric
+//                stage, signal, peers GET) - here the direction is PUT: quantise once, store to all.
+//
+// Arithmetic per 32-element block (bit-exact with the reference's CPU golden, "native" rounding):
+//   E = biased exponent of the largest |x|;  scale byte = E - 8;  code = RNE_sat_E4M3(x * 2^(127 - byte)).
+//   Blocks whose largest |x| is below 1e-12 follow the golden (scale byte 0x7F, signed-zero codes) or,
+//   with kDeviceTiny, the reference device kernel (byte = max(E - 8, 0)).  Inf/NaN blocks: 0xFF / 0x7F.
+#pragma once
+
+#include "common.cuh"
+
+namespace catccos {
+
+constexpr uint32_t kQuantThreads = 256;
+constexpr uint32_t kQuantRowsPerItem = 16;  // == kRowsPerChunk of the GEMM gate: 8 warps x 2 rows
+constexpr uint32_t kQuantColsPerWarpStep = 512;
+
+struct QuantPushParams {
+    // producer: this rank's shard
+    const void* in;           // bf16 [M, K]  (or, for the pre-quantised push, E4M3 codes [M, K])
+    const uint8_t* in_scales; // pre-quantised push only: E8M0 [M, K/32]
+    uint32_t M, K;
+    uint32_t produce;         // 0: skip the producer part (the harness that runs the two parts apart)
+    uint32_t publish;         // 0: nobody waits on this shard's flags (single rank, plain quantise)
+    uint32_t rank, world, epoch;
+    uint32_t segs_per_chunk;  // a 16-row chunk is split into this many column segments (work items)
+    uint32_t seg_cols;        // columns per segment (multiple of 512)
+    uint32_t num_dst;
+    uint8_t* dst_codes[kMaxRanks];   // where this shard's codes [M, K] go at destination d
+    uint8_t* dst_scales[kMaxRanks];  // where this shard's scales [M, K/32] go at destination d
+    uint32_t* dst_flags[kMaxRanks];  // destination d's flag words for this source (one per chunk) or nullptr
+    uint32_t* counters;              // local, one per chunk, zero between calls (segs_per_chunk > 1 only)
+    // consumer (standalone quantise + allgather with outputs outside symmetric memory):
+    // copy the peers' shards from this GPU's stage to the caller's outputs as their flags arrive
+    uint32_t consume;
+    const uint8_t* stage_codes;   // [world][M][K]
+    const uint8_t* stage_scales;  // [world][M][K/32]
+    uint8_t* out_codes;           // [world * M, K]
+    uint8_t* out_scales;          // [world * M, K/32]
+    const uint32_t* flags;        // this GPU's flag words [world][flag_stride]
+    uint32_t flag_stride;
+    uint64_t timeout_ns;
+    StatusBlock* status;
+};
+
+__device__ __forceinline__ uint32_t absmax_bits8(uint4 v)
+{
+    uint32_t m = __vmaxu2(__vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu), __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
+    return max(m & 0xFFFFu, m >> 16);
+}
+
+// two fp32 -> two E4M3 codes (round to nearest even, saturate to +-448), first value in the low byte
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t encode4(uint32_t a, uint32_t b, float mul)
+{
+    const float a0 = __uint_as_float(a << 16) * mul, a1 = __uint_as_float(a & 0xFFFF0000u) * mul;
+    const float b0 = __uint_as_float(b << 16) * mul, b1 = __uint_as_float(b & 0xFFFF0000u) * mul;
+    return cvt_e4m3x2(a0, a1) | (cvt_e4m3x2(b0, b1) << 16);
+}
+
+// Scale byte and multiplier for a block whose largest |bf16 bits| is amax.
+template <bool kDeviceTiny>
+__device__ __forceinline__ void block_scale(uint32_t amax, uint32_t& byte, float& mul, bool& nonfinite)
+{
+    const uint32_t E = amax >> 7;
+    nonfinite = (E == 0xFFu);
+    if (kDeviceTiny) {
+        byte = E > 8u ? E - 8u : 0u;
+        mul = byte == 0u ? 0.0f : __uint_as_float((254u - byte) << 23);
+    } else {
+        const bool tiny = amax <= 0x2B8Cu;  // |x| < 1e-12 for every bf16 in the block
+        byte = tiny ? 0x7Fu : E - 8u;
+        mul = tiny ? 0.0f : __uint_as_float((254u - byte) << 23);
+    }
+    if (nonfinite) {
+        byte = 0xFFu;
+    }
+}
+
+// Quantises 16 bf16 values held by one lane (two lanes share a 32-block).
+template <bool kDeviceTiny>
+__device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, uint32_t& byte)
+{
+    uint32_t amax = max(absmax_bits8(v0), absmax_bits8(v1));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    float mul;
+    bool nonfinite;
+    block_scale<kDeviceTiny>(amax, byte, mul, nonfinite);
+    uint4 o;
+    o.x = encode4(v0.x, v0.y, mul);
+    o.y = encode4(v0.z, v0.w, mul);
+    o.z = encode4(v1.x, v1.y, mul);
+    o.w = encode4(v1.z, v1.w, mul);
+    if (nonfinite) {
+        o = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+    }
+    return o;
+}
+
+// Publishes a finished chunk: every thread's stores are ordered before the flag words.
+__device__ __forceinline__ void publish_chunk(const QuantPushParams& p, uint32_t chunk)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        bool last = true;
+        if (p.segs_per_chunk > 1) {
+            const uint32_t old = atomicAdd(p.counters + chunk, 1u);
+            last = (old == p.segs_per_chunk - 1);
+            if (last) {
+                p.counters[chunk] = 0;
+                __threadfence_system();
+            }
+        }
+        if (last) {
+#pragma unroll
+            for (uint32_t d = 0; d < (uint32_t)kMaxRanks; ++d) {
+                if (d < p.num_dst && p.dst_flags[d] != nullptr) {
+                    st_release_sys(p.dst_flags[d] + chunk, p.epoch);
+                }
+            }
+        }
+    }
+}
+
+template <bool kDeviceTiny, bool kPreQuantised>
+__global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
+{
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t items = p.produce ? chunks * p.segs_per_chunk : 0u;
+    const uint32_t sf_cols = p.K / 32;
+    const bool sf_vec = (sf_cols % 4u) == 0u;
+
+    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const uint32_t chunk = item / p.segs_per_chunk;
+        const uint32_t seg = item - chunk * p.segs_per_chunk;
+        const uint32_t c_begin = seg * p.seg_cols;
+        const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
+        const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
+
+        for (uint32_t cb = c_begin; cb < c_end; cb += kQuantColsPerWarpStep) {
+            const uint32_t col = cb + lane * 16;
+            const bool col_ok = col < c_end;
+            uint4 v[2][2];
+            uint4 o[2];
+            uint32_t byte[2];
+            // loads for both rows first (four 16-byte loads in flight per lane)
+#pragma unroll
+            for (uint32_t r = 0; r < 2; ++r) {
+                const uint32_t row = row0 + r;
+                v[r][0] = v[r][1] = make_uint4(0, 0, 0, 0);
+                if (col_ok && row < p.M) {
+                    if (kPreQuantised) {
+                        v[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
+                                                                       (size_t)row * p.K + col));
+                    } else {
+                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.in) +
+                                                                          (size_t)row * p.K + col);
+                        v[r][0] = __ldcs(src);
+                        v[r][1] = __ldcs(src + 1);
+                    }
+                }
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < 2; ++r) {
+                const uint32_t row = row0 + r;
+                if (kPreQuantised) {
+                    o[r] = v[r][0];
+                    byte[r] = 0;
+                    if (col_ok && row < p.M && (lane & 1u) == 0u) {
+                        byte[r] = p.in_scales[(size_t)row * sf_cols + col / 32];
+                    }
+                } else {
+                    o[r] = quant16<kDeviceTiny>(v[r][0], v[r][1], byte[r]);
+                }
+                // scale bytes of 8 lanes (4 blocks) packed into one word on lanes 0, 8, 16, 24
+                const uint32_t base = lane & ~7u;
+                uint32_t w = __shfl_sync(0xFFFFFFFFu, byte[r], base) |
+                             (__shfl_sync(0xFFFFFFFFu, byte[r], base + 2) << 8) |
+                             (__shfl_sync(0xFFFFFFFFu, byte[r], base + 4) << 16) |
+                             (__shfl_sync(0xFFFFFFFFu, byte[r], base + 6) << 24);
+                if (col_ok && row < p.M) {
+                    const size_t code_off = (size_t)row * p.K + col;
+                    const size_t sf_off = (size_t)row * sf_cols + col / 32;
+#pragma unroll
+                    for (uint32_t d = 0; d < (uint32_t)kMaxRanks; ++d) {
+                        if (d >= p.num_dst || p.dst_codes[d] == nullptr) {
+                            continue;
+                        }
+                        *reinterpret_cast<uint4*>(p.dst_codes[d] + code_off) = o[r];
+                        if (sf_vec) {
+                            if ((lane & 7u) == 0u) {
+                                *reinterpret_cast<uint32_t*>(p.dst_scales[d] + sf_off) = w;
+                            }
+                        } else if ((lane & 1u) == 0u) {
+                            p.dst_scales[d][sf_off] = (uint8_t)byte[r];
+                        }
+                    }
+                }
+            }
+        }
+        if (p.publish) {
+            publish_chunk(p, chunk);
+        }
+    }
+
+    if (!p.consume) {
+        return;
+    }
+    // ---- consumer: stage -> caller's outputs, chunk by chunk as the peers' flags arrive ----
+    const uint32_t peer_items = (p.world - 1) * chunks;
+    for (uint32_t item = blockIdx.x; item < peer_items; item += gridDim.x) {
+        const uint32_t chunk = item / (p.world - 1);
+        const uint32_t src = (p.rank + 1 + item % (p.world - 1)) % p.world;
+        if (threadIdx.x == 0) {
+            if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk, p.epoch, p.timeout_ns)) {
+                report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
+            }
+        }
+        __syncthreads();
+        const uint32_t r_begin = chunk * kQuantRowsPerItem;
+        const uint32_t r_end = min(p.M, r_begin + kQuantRowsPerItem);
+        const size_t shard = (size_t)src * p.M;
+        // codes: rows are contiguous in both buffers, so the chunk is one flat span
+        {
+            const size_t off = (shard + r_begin) * p.K;
+            const size_t bytes = (size_t)(r_end - r_begin) * p.K;
+            const uint4* s = reinterpret_cast<const uint4*>(p.stage_codes + off);
+            uint4* d = reinterpret_cast<uint4*>(p.out_codes + off);
+            for (size_t i = threadIdx.x; i < bytes / 16; i += kQuantThreads) {
+                __stcs(d + i, __ldcg(s + i));
+            }
+        }
+        {
+            const size_t off = (shard + r_begin) * sf_cols;
+            const size_t bytes = (size_t)(r_end - r_begin) * sf_cols;
+            if (((off | bytes) & 3u) == 0u) {
+                const uint32_t* s = reinterpret_cast<const uint32_t*>(p.stage_scales + off);
+                uint32_t* d = reinterpret_cast<uint32_t*>(p.out_scales + off);
+                for (size_t i = threadIdx.x; i < bytes / 4; i += kQuantThreads) {
+                    d[i] = __ldcg(s + i);
+                }
+            } else {
+                for (size_t i = threadIdx.x; i < bytes; i += kQuantThreads) {
+                    p.out_scales[off + i] = __ldcg(p.stage_scales + off + i);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace catccos

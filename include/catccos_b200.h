@@ -1,0 +1,129 @@
+/*
+ * C ABI of libcatccos_b200.so: the B200 (sm_100a) implementation of CATCCOS's MXFP8
+ * quantise + AllGather and AllGather-Matmul operators.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns 0 on success
+ * or a negative CATCCOS_B200_E* code.  Device errors that can only be seen after the stream has
+ * run (a peer that never published a chunk) are read with catccos_b200_last_status().
+ * Each comment names the reference interface the entry point stands in for
+ * (paths are relative to the reference repository).
+ */
+#ifndef CATCCOS_B200_H
+#define CATCCOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same 17 x uint32 layout as CocTilingParams (utils/info.h:97-115); the operators read
+ * m, k, n and rankSize, the remaining fields are accepted for source compatibility. */
+typedef struct catccos_b200_tiling {
+    uint32_t m, k, n, transA, transB, m0, k0, n0;
+    uint32_t commTileM, commInterval, commNpuSplit, commDataSplit, commBlockM;
+    uint32_t rankSize, epSize, expertNum, topK;
+} catccos_b200_tiling_t;
+
+enum {
+    CATCCOS_B200_OK = 0,
+    CATCCOS_B200_EINVAL = -1,   /* bad shape / argument (N % 32, K % 128, rank count, null pointer) */
+    CATCCOS_B200_ESTATE = -2,   /* not initialised, or initialised differently */
+    CATCCOS_B200_ECUDA = -3,    /* a CUDA runtime or driver call failed (printed as "cudaError:<n>") */
+    CATCCOS_B200_ENOMEM = -4,   /* symmetric buffer too small for the problem */
+    CATCCOS_B200_ENET = -5,     /* rendezvous failed (connect / accept / handle exchange) */
+    CATCCOS_B200_ENOTSYMM = -6, /* pointer is not inside a buffer from catccos_b200_symm_alloc */
+    CATCCOS_B200_ETIMEOUT = -7  /* a device-side wait ran out (see catccos_b200_last_status) */
+};
+
+/* ---- process set-up ------------------------------------------------------------------------
+ * One process per rank.  Stands in for aclInit + aclrtSetDevice + set_attr + aclshmemx_init_attr
+ * (examples/ascend950_mx_quant_allgather/main.cpp:145-153, utils/shmem_init.h:18-45).
+ * ip_port is the reference's rendezvous string, e.g. "tcp://127.0.0.1:8789".  world == 1 needs
+ * no rendezvous (ip_port may be NULL). */
+int catccos_b200_init(int rank, int world, int device, const char* ip_port);
+
+/* Single-process harness: this process hosts all `world` ranks, rank r on devices[r] (devices may
+ * repeat: several ranks on one GPU, used to exercise the multi-rank protocol on one device).
+ * catccos_b200_set_rank chooses the rank the next calls act as. */
+int catccos_b200_init_local(int world, const int* devices);
+int catccos_b200_set_rank(int rank);
+
+/* shmem_finalize + aclrtResetDevice + aclFinalize (main.cpp:221-224). */
+int catccos_b200_finalize(void);
+
+/* aclshmem_calloc(1, bytes) (main.cpp:169): collective, zero-filled, mapped into every rank.
+ * With one process per rank the memory is a cuMem/VMM allocation exported to the peers. */
+int catccos_b200_symm_alloc(size_t bytes, void** local_ptr);
+/* shmem_free (main.cpp:219). */
+int catccos_b200_symm_free(void* local_ptr);
+/* CatccosOperator::GetSymmetricSize (utils/catccos_operator.h:43): bytes the two operators need
+ * for a problem (header + two stages of the gathered codes and scales). */
+size_t catccos_b200_symm_bytes_needed(const catccos_b200_tiling_t* tiling, int quant_op);
+
+/* ---- operators -----------------------------------------------------------------------------
+ * `stream` is a cudaStream_t.  `magic` is accepted and unused, as in the reference
+ * (mx_quant_allgather_device.h:111-112). */
+
+/* MxQuantAllGather<bf16, RowMajor, E4M3, RowMajor><<<rankSize, stream>>>(ffts, in, out, scale,
+ * symm, tiling, magic) (examples/ascend950_mx_quant_allgather/mx_quant_allgather_device.h:108-141,
+ * main.cpp:186).  The quantised axis is tiling->n (mx_quant_allgather_host.h:30-44):
+ * in bf16 [m, n]; out_codes uint8 [rankSize*m, n]; out_scales uint8 [rankSize*m, n/32]. */
+int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out_codes, void* out_scales, void* symm,
+                                    const catccos_b200_tiling_t* tiling, uint32_t magic);
+
+/* DeviceDGemm<MxAllGatherMatmulTla>::Arguments + Initialize + Run
+ * (include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:121-135,
+ * include/catccos/dgemm/device/device_dgemm.hpp:77,116): A already quantised.
+ * a E4M3 [m, k]; a_scale E8M0 [m, k/32]; b E4M3 [k, n]; b_scale E8M0 [k/64, n, 2];
+ * c [rankSize*m, n] (bf16 by default, fp16 with option "c_dtype" = 1). */
+int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void* b, const void* a_scale,
+                                         const void* b_scale, void* c, void* symm,
+                                         const catccos_b200_tiling_t* tiling, uint32_t magic);
+
+/* The fused form of the two operators above (quantise kernel pushes, GEMM kernel consumes as
+ * chunks land): a bf16 [m, k] quantised on the fly, everything else as above.  The reference has
+ * no single entry point for it; it is MxQuantAllGather feeding MxAllGatherMatmulTla. */
+int catccos_b200_mx_quant_allgather_matmul(void* stream, const void* a_bf16, const void* b, const void* b_scale,
+                                           void* c, void* symm, const catccos_b200_tiling_t* tiling, uint32_t magic);
+
+/* ---- single-GPU building blocks (the compute halves, also the unfused baseline) ------------ */
+
+/* CommBlockMxQuant::operator() (include/catccos/comm/block/comm_block_mx_quant.hpp:155-207):
+ * bf16 [rows, k] -> codes [rows, k] + scales [rows, k/32], no communication. */
+int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint32_t k, void* codes, void* scales);
+
+/* BlockMmadTla<MmadMx> main loop on data that is already gathered
+ * (ascend950_fp8_mx_allgather_matmul_device.h:47-57): c [m, n] = dequant(a)[m, k] x dequant(b)[k, n]. */
+int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,
+                         uint32_t m, uint32_t n, uint32_t k);
+
+/* Transposed copy of a weight, b [k, n] -> bt [n, k], for option "b_layout" = 1.  No reference
+ * counterpart: the reference reads B through CATLASS layout tags (mx_allgather_matmul.hpp:148-151). */
+int catccos_b200_transpose_weight(void* stream, const void* b, void* bt, uint32_t k, uint32_t n);
+
+/* ---- status and options ---------------------------------------------------------------------
+ * out[0] code (0 ok, 1 ready-flag timeout, 2 internal barrier timeout, 3 handshake timeout),
+ * out[1] rank waited for, out[2] chunk, out[3] epoch.  Synchronises the device, clears the record.
+ * The reference has no counterpart: its waits are unbounded (mx_quant_allgather.hpp:179-185). */
+int catccos_b200_last_status(uint32_t out[4]);
+
+/* Options (all ranks must set the same values):
+ *   "tiny_block_rule" 0 = CPU golden (amax < 1e-12 -> scale 0x7F), 1 = reference device kernel
+ *   "c_dtype"         0 = bf16, 1 = fp16 (the reference's output type, main.cpp:28)
+ *   "b_layout"        0 = b is [k, n] as in the reference files, 1 = b is the transposed copy [n, k]
+ *   "block_n"         0 = automatic, 128 or 256 = GEMM tile width
+ *   "timeout_ms"      limit of device-side waits on peers (default 2000)
+ *   "phase_mask"      bit 0 = launch the producer side, bit 1 = launch the consumer side (default 3);
+ *                     the single-GPU harness runs all ranks' producers before any consumer. */
+int catccos_b200_set_option(const char* key, int64_t value);
+
+/* Number of kernels this library has launched since it was loaded. */
+uint64_t catccos_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CATCCOS_B200_H */

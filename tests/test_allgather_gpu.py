@@ -1,0 +1,168 @@
+"""GPU tests of the multi-rank protocol on ONE device: the single-process harness hosts all ranks,
+runs every rank's producer kernel first and the consumers afterwards (kernels of different ranks
+never wait on one another while sharing a GPU).  Results are compared with the oracle: gathered codes
+and scales bit for bit, GEMM output within rtol 1e-2 / atol 1e-3."""
+import numpy as np
+import pytest
+
+from catccos_b200 import workloads
+from conftest import to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def local_world(capi, cuda):
+    made = {}
+
+    def _make(world):
+        capi.finalize()
+        capi.init_local(world, [0] * world)
+        made["w"] = world
+        return world
+
+    yield _make
+    capi.set_option("phase_mask", 3)
+    capi.set_option("timeout_ms", 2000)
+    capi.finalize()
+
+
+def _alloc_symm(capi, world, nbytes):
+    ptrs = []
+    for r in range(world):
+        capi.set_rank(r)
+        ptrs.append(capi.symm_alloc(nbytes))
+    return ptrs
+
+
+def _quant_allgather_round(capi, torch, xs, outs, symm, world):
+    for phase in (1, 2):
+        capi.set_option("phase_mask", phase)
+        for r in range(world):
+            capi.set_rank(r)
+            capi.mx_quant_allgather(xs[r], outs[r][0], outs[r][1], symm[r], world)
+    torch.cuda.synchronize()
+    capi.set_option("phase_mask", 3)
+    for r in range(world):
+        capi.set_rank(r)
+        code, st = capi.last_status()
+        assert code == 0, (r, st)
+
+
+@pytest.mark.parametrize("world,m,k", [(2, 64, 1024), (4, 126, 512), (3, 37, 160), (8, 16, 7168)])
+def test_quant_allgather_emulated(capi, cuda, oracle, local_world, world, m, k):
+    torch = cuda
+    local_world(world)
+    t = capi.make_tiling(m, 1, k, world)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(t, True))
+    rng = np.random.default_rng(world * 1000 + m)
+    for rnd in range(3):  # three rounds: both stages and the reuse of the first
+        bits = [workloads.f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)) for _ in range(world)]
+        xs = [to_dev_bf16(torch, b) for b in bits]
+        outs = [(torch.full((world * m, k), 0xAA, dtype=torch.uint8, device="cuda"),
+                 torch.full((world * m, k // 32), 0xAA, dtype=torch.uint8, device="cuda")) for _ in range(world)]
+        _quant_allgather_round(capi, torch, xs, outs, symm, world)
+        want = [oracle.quantize_rows(b) for b in bits]
+        want_c = np.concatenate([w[0] for w in want])
+        want_s = np.concatenate([w[1] for w in want])
+        for r in range(world):
+            assert np.array_equal(outs[r][0].cpu().numpy(), want_c), (rnd, r)
+            assert np.array_equal(outs[r][1].cpu().numpy(), want_s), (rnd, r)
+
+
+def _agmm_round(capi, torch, call, world):
+    for phase in (1, 2):
+        capi.set_option("phase_mask", phase)
+        for r in range(world):
+            capi.set_rank(r)
+            call(r)
+    torch.cuda.synchronize()
+    capi.set_option("phase_mask", 3)
+    for r in range(world):
+        capi.set_rank(r)
+        code, st = capi.last_status()
+        assert code == 0, (r, st)
+
+
+@pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272)])
+def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n):
+    torch = cuda
+    local_world(world)
+    t = capi.make_tiling(m, k, n, world)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(t, False))
+    cfg = workloads.Config("t", m, k, n, (world,), "normal", "")
+    for rnd in range(2):
+        a_bits = [workloads.activation_bits(cfg, r, seed=rnd) for r in range(world)]
+        w = [oracle.quantize_weight(workloads.weight_bits(cfg, r, seed=rnd)) for r in range(world)]
+        a_d = [to_dev_bf16(torch, b) for b in a_bits]
+        b_d = [(torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()) for bc, bs in w]
+        c_d = [torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        _agmm_round(capi, torch,
+                    lambda r: capi.mx_quant_allgather_matmul(a_d[r], b_d[r][0], b_d[r][1], c_d[r], symm[r], world),
+                    world)
+        aq = [oracle.quantize_rows(b) for b in a_bits]
+        for r in range(world):
+            gold = oracle.allgather_matmul([q[0] for q in aq], [q[1] for q in aq], w[r][0], w[r][1])
+            bad, maxdiff = oracle.check_close(c_d[r].float().cpu().numpy(), gold, 1e-2, 1e-3)
+            assert bad == 0, (rnd, r, bad, maxdiff)
+
+
+def test_prequantised_allgather_matmul_emulated(capi, cuda, oracle, local_world, golden):
+    # the reference's operator signature: A arrives quantised, in the reference's file layouts
+    torch = cuda
+    d = golden("agmm_small")
+    world, m, k = d["a_codes"].shape
+    n = d["b_codes"].shape[1]
+    local_world(world)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(capi.make_tiling(m, k, n, world), False))
+    a_d = [(torch.from_numpy(d["a_codes"][r]).cuda(), torch.from_numpy(d["a_scales"][r]).cuda()) for r in range(world)]
+    b_d, bs_d = torch.from_numpy(d["b_codes"]).cuda(), torch.from_numpy(d["b_scales"]).cuda()
+    c_d = [torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    _agmm_round(capi, torch,
+                lambda r: capi.fp8_mx_allgather_matmul(a_d[r][0], a_d[r][1], b_d, bs_d, c_d[r], symm[r], world), world)
+    for r in range(world):
+        bad, maxdiff = oracle.check_close(c_d[r].float().cpu().numpy(), d["golden"], 1e-2, 1e-3)
+        assert bad == 0, (r, bad, maxdiff)
+
+
+def test_fused_single_rank_two_streams(capi, cuda, oracle):
+    # world 1 through the production path: quantise kernel on the side stream, GEMM gated on its flags
+    torch = cuda
+    capi.finalize()
+    cfg = workloads.Config("t", 640, 1024, 768, (1,), "normal", "")
+    a_bits = workloads.activation_bits(cfg, 0, seed=7)
+    bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=7))
+    symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(cfg.m_local, cfg.k, cfg.n_local, 1), False))
+    a_d = to_dev_bf16(torch, a_bits)
+    b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
+    c_d = torch.zeros((cfg.m_local, cfg.n_local), dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        capi.mx_quant_allgather_matmul(a_d, b_d, bs_d, c_d, symm, 1)
+    code, st = capi.last_status()
+    assert code == 0, st
+    ac, asc = oracle.quantize_rows(a_bits)
+    gold = oracle.allgather_matmul([ac], [asc], bc, bs)
+    bad, maxdiff = oracle.check_close(c_d.float().cpu().numpy(), gold, 1e-2, 1e-3)
+    assert bad == 0, (bad, maxdiff)
+    capi.symm_free(symm)
+
+
+def test_missing_peer_is_reported_not_hung(capi, cuda, local_world):
+    # failure detection without a GPU fault: rank 1 never launches its producer, so rank 0's
+    # consumer waits on flags that nothing sets; the bounded wait runs out, the kernel ends and the
+    # status names the rank and chunk it was waiting for
+    torch = cuda
+    world, m, k = 2, 32, 256
+    local_world(world)
+    capi.set_option("timeout_ms", 100)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(capi.make_tiling(m, 1, k, world), True))
+    x = torch.zeros((m, k), dtype=torch.bfloat16, device="cuda")
+    oc = torch.zeros((world * m, k), dtype=torch.uint8, device="cuda")
+    osc = torch.zeros((world * m, k // 32), dtype=torch.uint8, device="cuda")
+    capi.set_rank(0)
+    capi.mx_quant_allgather(x, oc, osc, symm[0], world)  # producer and consumer of rank 0 only
+    code, st = capi.last_status()
+    assert code == -7 and st[0] == 1 and st[1] == 1 and st[3] == 1, (code, st)
+    # the context is still usable and the record was cleared
+    assert torch.zeros(4, device="cuda").sum().item() == 0
+    assert capi.last_status()[0] == 0

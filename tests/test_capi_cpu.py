@@ -1,0 +1,42 @@
+"""CPU tests of the drop-in boundary: the shared library loads without a GPU and exports every
+symbol the header declares; argument checks that need no device."""
+import ctypes
+import os
+import re
+
+from conftest import ROOT
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "catccos_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(catccos_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(capi):
+    lib = capi.load()
+    names = _declared()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(capi.EXPORTS) == names
+
+
+def test_tiling_struct_matches_reference_layout(capi):
+    assert ctypes.sizeof(capi.Tiling) == 17 * 4
+    assert [f[0] for f in capi.Tiling._fields_][:3] == ["m", "k", "n"]
+    assert capi.Tiling.rankSize.offset == 13 * 4
+
+
+def test_symm_bytes_needed(capi):
+    t = capi.make_tiling(4096, 1, 7168, 8)
+    need = capi.symm_bytes_needed(t, True)
+    data = 8 * 4096 * (7168 + 224)
+    assert 2 * data < need < 2 * data + (2 << 20)
+    assert need < 1004 * 1024 * 1024  # fits the reference's SHMEM_BUFF_BYTES (utils/info.h:36)
+
+
+def test_set_option_rejects_unknown(capi):
+    assert capi.load().catccos_b200_set_option(b"no_such_option", 1) == -1
+    assert capi.load().catccos_b200_set_option(b"block_n", 192) == -1
+    assert capi.load().catccos_b200_set_option(b"block_n", 0) == 0
