@@ -1,0 +1,374 @@
+#!/usr/bin/env python
+"""Benchmark of the MXFP8 quantise + AllGather-Matmul path on N B200 GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...                      (the CPU golden path on the host cores)
+
+A step is one fused call (quantise-and-push kernel + flag-gated tcgen05 GEMM kernel) on the
+TP prefill workload: per rank A bf16 [1024, 7168] quantised on the fly, weight shard MXFP8
+[7168, 2304], output bf16 [N * 1024, 2304].  Per-rank shapes are fixed as N grows (weak scaling).
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from catccos_b200 import workloads  # noqa: E402
+
+CFG = workloads.CONFIGS["c3_prefill"]
+QCFG = workloads.CONFIGS["c2_quant_ag"]
+METRIC = "mxfp8_allgather_matmul_tflops"
+UNIT = "TFLOP/s"
+FP8_NOMINAL_TFLOPS = 4500.0
+NVLINK_NOMINAL_GBS = 900.0
+# dram bytes per launch of the dominant kernel, from the committed ncu summary (profiles/); None = not captured
+GEMM_DRAM_TRAFFIC_BYTES_N1 = None
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def workload_config(world: int) -> dict:
+    return {
+        "workload": "c3_prefill MXFP8 AllGather-Matmul (TP prefill shape)",
+        "m_local": CFG.m_local, "k": CFG.k, "n_local": CFG.n_local, "world": world,
+        "a": "bf16 N(0,1), quantised on the fly to E4M3 + E8M0 per 32 along K",
+        "b": "E4M3 [K, N_local] + E8M0 [K/64, N_local, 2], from bf16 N(0,0.02)",
+        "c": "bf16 [world*m_local, n_local], fp32 accumulate",
+        "l2": "flushed between timed steps (256 MiB write)",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference's golden path; the only part of this file that touches oracle/)
+# ------------------------------------------------------------------------------------------------
+def cpu_golden_step(world: int, rows_per_rank: int, a_f32, b_deq, torch):
+    from oracle import mx_oracle
+
+    return mx_oracle.golden_allgather_matmul_torch([a[:rows_per_rank] for a in a_f32[:world]], b_deq)
+
+
+def cpu_problem(world: int, torch):
+    from oracle import mx_oracle
+
+    a_f32 = [torch.from_numpy(workloads.bf16_bits_to_f32(workloads.activation_bits(CFG, r, seed=0)).copy())
+             for r in range(world)]
+    bc, bs = mx_oracle.quantize_weight(workloads.weight_bits(CFG, 0, seed=0))
+    b_deq = torch.from_numpy(mx_oracle.dequant_weight(bc, bs))
+    return a_f32, b_deq
+
+
+def run_cpu_baseline(world: int, budget_s: float = 12.0) -> dict:
+    """Times the torch-CPU port of the reference golden (quantise every rank's A, dequantise, fp32
+    matmul) for one rank's problem on all host cores."""
+    import torch
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    a_f32, b_deq = cpu_problem(world, torch)
+    cpu_golden_step(world, CFG.m_local, a_f32, b_deq, torch)  # warm-up
+    reps, t0 = 0, time.perf_counter()
+    while reps < 5 and (time.perf_counter() - t0) < budget_s:
+        cpu_golden_step(world, CFG.m_local, a_f32, b_deq, torch)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    flops = workloads.gemm_flops(CFG, world)
+    return {
+        "value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"one rank's full problem at world {world} ({world}x quantise [1024,7168] + fp32 matmul "
+                  f"[{world * CFG.m_local},7168]x[7168,2304]), {reps} repetitions, {dt * 1e3:.1f} ms each",
+    }
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    world = args.gpus
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    a_f32, b_deq = cpu_problem(world, torch)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_golden_step(world, CFG.m_local, a_f32, b_deq, torch)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_golden_step(world, CFG.m_local, a_f32, b_deq, torch)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = workloads.gemm_flops(CFG, world) / dt / 1e12
+    sample = (f"every step is one rank's full problem at world {world}: quantise {world} x [1024,7168], "
+              f"dequantise, fp32 torch.matmul [{world * CFG.m_local},7168]x[7168,2304] on {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (dequantised E4M3 x E8M0)", "data": "synthetic", "config": workload_config(world),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid: str):
+        self.uuid, self.proc, self.path = uuid, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx = float(parts[1])
+                except ValueError:
+                    continue
+                for nm, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def run_gpu(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from catccos_b200 import build, capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the GPU arm")
+    torch.cuda.set_device(local_rank)
+    if rank == 0:
+        build.build()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+        port = int(os.environ.get("MASTER_PORT", "29500")) + 211
+        capi.init(rank, world, local_rank, f"tcp://127.0.0.1:{port}")
+    else:
+        capi.init(0, 1, local_rank, None)
+    dev = torch.device("cuda", local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- data (seeded, resident in HBM before the timed region) ----
+    a_bits = workloads.activation_bits(CFG, rank, seed=0)
+    a_host = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+    a_dev = a_host.to(dev, non_blocking=False)
+    # the weight shard is quantised by the library's own kernel on the transposed weight (blocks of 32 run
+    # along K): B^T [N, K] rows -> codes [N, K], scales [N, K/32]; stored as [K, N] / [K/64, N, 2]
+    w_bits = workloads.weight_bits(CFG, rank, seed=0)
+    wt = torch.from_numpy(np.ascontiguousarray(w_bits.T).view(np.int16).copy()).to(dev).view(torch.bfloat16)
+    wc, ws = capi.mx_quant(wt)
+    b_codes = wc.t().contiguous()
+    b_scales = ws.t().contiguous().view(CFG.k // 64, 2, CFG.n_local).permute(0, 2, 1).contiguous()
+    del wt, wc, ws
+    c_dev = torch.empty((world * CFG.m_local, CFG.n_local), dtype=torch.bfloat16, device=dev)
+    c_host = torch.empty((world * CFG.m_local, CFG.n_local), dtype=torch.bfloat16).pin_memory()
+    tiling = capi.make_tiling(CFG.m_local, CFG.k, CFG.n_local, world)
+    symm = capi.symm_alloc(capi.symm_bytes_needed(tiling, False))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        capi.mx_quant_allgather_matmul(a_dev, b_codes, b_scales, c_dev, symm, world)
+
+    def timed(fn, steps, warmup, flush_l2=True):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for e0, e1 in evs:
+            if flush_l2:
+                flush.fill_(1)
+            e0.record()
+            fn()
+            e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) for e0, e1 in evs], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # per step: the slowest rank
+        return ms.cpu().numpy()
+
+    warmup = max(args.warmup, 3)
+    uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+    sampler = ClockSampler("GPU-" + uuid if not uuid.startswith("GPU-") else uuid)
+    launches0 = capi.launch_count()
+    if rank == 0:
+        sampler.start()
+    ms = timed(step, args.steps, warmup)
+    launches = capi.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    code, st = capi.last_status()
+    if code != 0:
+        raise SystemExit(f"device-side wait ran out: {st}")
+    ms_per_step = float(ms.mean())
+    flops_per_gpu = workloads.gemm_flops(CFG, world)
+    value = world * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers: H2D of A, fused call, D2H of C ----
+    def step_e2e():
+        a_dev.copy_(a_host, non_blocking=True)
+        step()
+        c_host.copy_(c_dev, non_blocking=True)
+
+    ms_e2e = timed(step_e2e, max(3, min(args.steps, 10)), 2)
+    e2e_value = world * flops_per_gpu / (float(ms_e2e.mean()) * 1e-3) / 1e12
+
+    # ---- extras: standalone quantise + allgather (GB/s), and the unfused baseline ----
+    extras = {}
+    try:
+        if args.lean:
+            raise RuntimeError("skipped (--lean)")
+        qa_bits = workloads.activation_bits(QCFG, rank, seed=0)
+        qa = torch.from_numpy(qa_bits.view(np.int16).copy()).to(dev).view(torch.bfloat16)
+        qt = capi.make_tiling(QCFG.m_local, 1, QCFG.k, world)
+        qsymm = capi.symm_alloc(capi.symm_bytes_needed(qt, True)) if world > 1 else 0
+        qc = torch.empty((world * QCFG.m_local, QCFG.k), dtype=torch.uint8, device=dev)
+        qs = torch.empty((world * QCFG.m_local, QCFG.k // 32), dtype=torch.uint8, device=dev)
+        q_ms = timed(lambda: capi.mx_quant_allgather(qa, qc, qs, qsymm, world), 10, 3)
+        q_us = float(np.median(q_ms)) * 1e3
+        extras["quant_allgather"] = {
+            "workload": f"c2 per rank bf16 [{QCFG.m_local},{QCFG.k}] at world {world}", "us": q_us,
+            "hbm_gbs": workloads.quant_ag_hbm_bytes(QCFG, world) / q_us / 1e3,
+            "nvlink_ingress_gbs": workloads.quant_ag_ingress_bytes(QCFG, world) / q_us / 1e3,
+            "frac_of_bound": (max(workloads.quant_ag_ingress_bytes(QCFG, world) / NVLINK_NOMINAL_GBS,
+                                  workloads.quant_ag_hbm_bytes(QCFG, world) / read_peaks()["hbm_gbs"]) / 1e3) / q_us,
+        }
+        del qa, qc, qs
+        # unfused: quantise, NCCL all-gather of codes and scales, then the same GEMM kernel on gathered data
+        g_codes = torch.empty((world * CFG.m_local, CFG.k), dtype=torch.uint8, device=dev)
+        g_scales = torch.empty((world * CFG.m_local, CFG.k // 32), dtype=torch.uint8, device=dev)
+
+        def unfused():
+            codes, scales = capi.mx_quant(a_dev)
+            if world > 1:
+                dist.all_gather_into_tensor(g_codes, codes)
+                dist.all_gather_into_tensor(g_scales, scales)
+                capi.mx_gemm(g_codes, g_scales, b_codes, b_scales, out=c_dev)
+            else:
+                capi.mx_gemm(codes, scales, b_codes, b_scales, out=c_dev)
+
+        u_ms = timed(unfused, 10, 3)
+        extras["unfused_baseline"] = {
+            "what": "quantise kernel, ncclAllGather of codes and of scales, GEMM kernel on local memory",
+            "ms_per_step": float(u_ms.mean()), "tflops_per_gpu": flops_per_gpu / (float(u_ms.mean()) * 1e-3) / 1e12,
+        }
+    except Exception as exc:  # the extras never take the headline number down with them
+        extras["extras_error"] = repr(exc)
+
+    peaks = read_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    per_gpu = flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+    t_compute = flops_per_gpu / (FP8_NOMINAL_TFLOPS * 1e12)
+    t_link = (world - 1) * CFG.m_local * (CFG.k + CFG.k // 32) / (NVLINK_NOMINAL_GBS * 1e9)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8 e4m3 x e8m0 block scales, fp32 accumulate, bf16 out", "data": "synthetic",
+        "config": workload_config(world),
+        "per_gpu_tflops": per_gpu,
+        "frac_of_nominal_roofline": max(t_compute, t_link) / (ms_per_step * 1e-3),
+        "roofline": {
+            "bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": UNIT, "frac": per_gpu / fp8_peak,
+            "traffic": GEMM_DRAM_TRAFFIC_BYTES_N1 if world == 1 else None,
+            "kernel": "mx_gemm_kernel (tcgen05.mma kind::mxf8f6f4.block_scale)",
+            "peak_source": f"2 x cuBLAS bf16 burst of {peaks['source']} ({peaks['bf16_tflops']} TFLOP/s); "
+                           "the peaks file holds no fp8 figure, fp8 issues at twice the bf16 rate",
+            "achieved_from": "2*(world*m_local)*k*n_local FLOP per launch / CUDA-event time of the step "
+                             "(the GEMM kernel spans the step; the quantise kernel runs beside it)",
+        },
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": float(ms_e2e.mean()),
+                "h2d_bytes_per_step": int(a_host.numel() * 2), "d2h_bytes_per_step": int(c_host.numel() * 2)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        **extras,
+    }
+    if rank == 0:
+        if world == 1 and not args.lean:
+            line["cpu_baseline"] = run_cpu_baseline(1)
+        print(json.dumps(line))
+    barrier()
+    capi.finalize()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--lean", action="store_true",
+                    help="headline loop only: no quant-allgather / unfused extras, no CPU baseline (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
