@@ -95,11 +95,9 @@ struct Driver {
 // state
 // ---------------------------------------------------------------------------------------------
 constexpr size_t kHeaderBytes = 1u << 20;       // counters + flag words at the start of a symmetric buffer
-constexpr size_t kCountersOff = 0;              // uint32 [kMaxChunks]
-constexpr uint32_t kMaxChunks = 24576;          // 16-row chunks per shard a buffer can flag
-constexpr size_t kFlagsOff = 256u << 10;        // uint32 [kMaxRanks][kMaxChunks]
-static_assert(kFlagsOff + (size_t)kMaxRanks * kMaxChunks * 4 <= kHeaderBytes, "header layout");
-static_assert(kMaxChunks * 4 <= kFlagsOff, "counter area");
+constexpr uint32_t kMaxFlags = 24576;           // flag words per source rank: (16-row chunks) x (K segments)
+constexpr size_t kFlagsOff = 256u << 10;        // uint32 [kMaxRanks][kMaxFlags]; the first 256 KiB are reserved
+static_assert(kFlagsOff + (size_t)kMaxRanks * kMaxFlags * 4 <= kHeaderBytes, "header layout");
 
 struct RankCtx {
     int device = 0;
@@ -138,6 +136,8 @@ struct State {
     int b_layout = 0;
     int block_n = 0;
     int phase_mask = 3;
+    int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
+    int quant_items_per_sm = 4;
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
 };
@@ -248,7 +248,7 @@ void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
 {
     const uint32_t chunks = (M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t max_segs = (K + kQuantColsPerWarpStep - 1) / kQuantColsPerWarpStep;
-    uint32_t want = ((uint32_t)num_sms * 4 + chunks - 1) / chunks;
+    uint32_t want = ((uint32_t)num_sms * (uint32_t)g.quant_items_per_sm + chunks - 1) / chunks;
     if (want < 1) want = 1;
     if (want > max_segs) want = max_segs;
     uint32_t seg_cols = (uint32_t)align_up((K + want - 1) / want, kQuantColsPerWarpStep);
@@ -271,6 +271,7 @@ int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool pre
     }
     if ((uint32_t)grid > items) grid = (int)items;
     p.produce = produce ? 1u : 0u;
+    p.sys_scope = g.publish_scope == 1 ? 1u : (g.publish_scope == 2 ? 0u : (p.world > 1 ? 1u : 0u));
     if (prequant) {
         mx_quant_push_kernel<false, true><<<grid, kQuantThreads, 0, st>>>(p);
     } else if (dev_tiny) {
@@ -330,7 +331,9 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     }
     uint32_t bn = (uint32_t)g.block_n;
     if (bn != 128 && bn != 256) {
-        bn = (p.N % 256 == 0 || p.N > 1024) ? 256 : 128;
+        // 256-wide tiles halve the A traffic per FLOP; take them when they still give every SM a tile
+        const uint32_t tiles256 = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + 255) / 256);
+        bn = (p.N > 128 && tiles256 >= (uint32_t)rc.num_sms) ? 256 : 128;
     }
     const bool b_mn = g.b_layout == 0;
     CUtensorMap ta, tb;
@@ -397,13 +400,15 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         ERROR_LOG("allgather matmul: symm must come from catccos_b200_symm_alloc");
         return CATCCOS_B200_ENOTSYMM;
     }
+    RankCtx& rc = cur();
     StageLayout L;
     const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
-    if (!stage_layout(sa->size, W, M, K, L) || chunks > kMaxChunks) {
+    QuantPushParams seg = {};
+    choose_segments(M, K, rc.num_sms, seg);  // the same split on every rank and in both kernels
+    if (!stage_layout(sa->size, W, M, K, L) || (size_t)chunks * seg.segs_per_chunk > kMaxFlags) {
         ERROR_LOG("allgather matmul: symmetric buffer of %zu bytes too small", sa->size);
         return CATCCOS_B200_ENOMEM;
     }
-    RankCtx& rc = cur();
     CUDA_TRY(cudaSetDevice(rc.device));
     cudaStream_t st = (cudaStream_t)stream;
     const bool produce = (g.phase_mask & 1) != 0, consume = (g.phase_mask & 2) != 0;
@@ -430,9 +435,8 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
             uint8_t* base = sa->base[d] + stage_off;
             q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
             q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
-            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxChunks;
+            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
         }
-        q.counters = reinterpret_cast<uint32_t*>(sa->base[rank] + kCountersOff);
         q.status = rc.status;
         q.timeout_ns = g.timeout_ns;
         cudaStream_t qs = consume ? rc.side : st;
@@ -456,7 +460,9 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         p.N = N;
         p.K = K;
         p.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
-        p.flag_stride = kMaxChunks;
+        p.flag_stride = kMaxFlags;
+        p.segs = seg.segs_per_chunk;
+        p.seg_ktiles = seg.seg_cols / kGemmBlockK;
         p.world = W;
         p.rank = rank;
         p.m_local = M;
@@ -804,7 +810,7 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
     }
     StageLayout L;
     const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
-    if (!stage_layout(sa->size, W, M, K, L) || chunks > kMaxChunks) {
+    if (!stage_layout(sa->size, W, M, K, L) || (size_t)chunks * q.segs_per_chunk > kMaxFlags) {
         ERROR_LOG("mx quant allgather: symmetric buffer of %zu bytes too small", sa->size);
         return CATCCOS_B200_ENOMEM;
     }
@@ -825,17 +831,16 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
             uint8_t* base = sa->base[d] + stage_off;
             q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
             q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
-            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxChunks;
+            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
         }
     }
-    q.counters = reinterpret_cast<uint32_t*>(sa->base[rank] + kCountersOff);
     q.consume = consume ? 1u : 0u;
     q.stage_codes = sa->base[rank] + stage_off + L.codes_off;
     q.stage_scales = sa->base[rank] + stage_off + L.scales_off;
     q.out_codes = oc;
     q.out_scales = os;
     q.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
-    q.flag_stride = kMaxChunks;
+    q.flag_stride = kMaxFlags;
     return launch_quant_push(rc, (cudaStream_t)stream, q, false, produce);
 }
 
@@ -929,6 +934,10 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.timeout_ns = (uint64_t)value * 1000000ull;
     } else if (k == "phase_mask" && value >= 1 && value <= 3) {
         g.phase_mask = (int)value;
+    } else if (k == "publish_scope" && value >= 0 && value <= 2) {
+        g.publish_scope = (int)value;
+    } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
+        g.quant_items_per_sm = (int)value;
     } else {
         ERROR_LOG("set_option: unknown key or bad value: %s = %lld", key, (long long)value);
         return CATCCOS_B200_EINVAL;

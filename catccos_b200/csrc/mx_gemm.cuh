@@ -12,13 +12,14 @@
 //   SFB    E8M0 bytes in the reference's file layout [K/64, N, 2]
 //   C      bf16 or fp16, row-major [Mg, N]
 //
-// One CTA per 128 x BLOCK_N output tile, persistent over tiles, 256 threads:
-//   warp 0    TMA producer: A and B tiles (128-byte swizzle) into a ring of shared-memory stages
-//   warp 1    MMA issuer: tcgen05.cp of the scale atoms into tensor memory, then four
+// One CTA per 128 x BLOCK_N output tile, persistent over tiles, 320 threads:
+//   warps 0-3 epilogue: tcgen05.ld of the fp32 accumulator, convert, 16-byte global stores
+//   warp 4    TMA producer: A and B tiles (128-byte swizzle) into a ring of shared-memory stages
+//   warp 5    MMA issuer: tcgen05.cp of the scale atoms into tensor memory, then four
 //             tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per stage
-//   warps 2-3 scale loaders: plain global loads of the E8M0 bytes, written to shared memory in
-//             the 32x16-byte atom layout tcgen05.cp expects
-//   warps 4-7 epilogue: tcgen05.ld of the fp32 accumulator, convert, 16-byte global stores
+//   warps 6-9 scale loaders: warp j serves every fourth K tile; plain global loads of the E8M0
+//             bytes (the next K tile's loads are in flight while the current one is stored),
+//             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects
 //
 // When `flags` is set, a tile is not touched before every (source rank, 16-row chunk) under its
 // rows has been published with the current epoch by the quantise-and-push kernel; tiles are
@@ -35,7 +36,8 @@ namespace catccos {
 
 constexpr uint32_t kGemmBlockM = 128;
 constexpr uint32_t kGemmBlockK = 128;   // bytes == elements (8-bit codes): one 128-byte swizzle row
-constexpr uint32_t kGemmThreads = 256;
+constexpr uint32_t kGemmThreads = 320;
+constexpr uint32_t kSfWarps = 4;
 constexpr uint32_t kRowsPerChunk = 16;  // granularity of the ready flags
 constexpr uint32_t kTmemCols = 512;
 
@@ -45,8 +47,10 @@ struct GemmParams {
     void* c;                  // [Mg, N]
     uint32_t Mg, N, K;
     // gating on the quantise-and-push kernel (flags == nullptr: all of A is already in place)
-    const uint32_t* flags;  // [world][flag_stride] epoch words in this GPU's symmetric header
+    const uint32_t* flags;  // [world][flag_stride] epoch words in this GPU's symmetric header,
+                            // word chunk * segs + seg covers 16 rows x (seg_ktiles * 128) columns of K
     uint32_t flag_stride;
+    uint32_t segs, seg_ktiles;
     uint32_t world, rank, m_local, epoch;
     uint64_t timeout_ns;
     StatusBlock* status;
@@ -111,8 +115,8 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, 
     return t;
 }
 
-// Waits (whole warp) until every chunk under gathered rows [m0, m0 + 128) carries the epoch.
-__device__ __forceinline__ void wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane)
+// Waits (whole warp) until K segment `seg` of every chunk under gathered rows [m0, m0 + 128) carries the epoch.
+__device__ __forceinline__ void wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane, uint32_t seg)
 {
     uint32_t prev_src = 0xFFFFFFFFu, prev_chunk = 0xFFFFFFFFu;
     for (uint32_t i = 0; i < 4; ++i) {
@@ -127,7 +131,7 @@ __device__ __forceinline__ void wait_rows_ready(const GemmParams& p, uint32_t m0
         }
         prev_src = src;
         prev_chunk = chunk;
-        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk, p.epoch, p.timeout_ns)) {
+        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk * p.segs + seg, p.epoch, p.timeout_ns)) {
             report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
         }
     }
@@ -181,7 +185,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full_ab[s], 1);
-            mbar_init(&full_sf[s], 2);
+            mbar_init(&full_sf[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (uint32_t a = 0; a < 2; ++a) {
@@ -193,7 +197,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
-    if (warp == 1) {
+    if (warp == 5) {
         tmem_alloc(tmem_ptr_smem, kTmemCols);
         tmem_relinquish();
     }
@@ -202,19 +206,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
-    if (warp == 0) {
+    if (warp == 4) {
         // ------------------------------- TMA producer -------------------------------------
         uint32_t it = 0;
         for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
-            if (p.flags != nullptr) {
-                wait_rows_ready(p, m0, lane);
-                fence_proxy_async_all();
-            }
-            if (lane == 0) {
-                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                if (p.flags != nullptr && kt % p.seg_ktiles == 0) {
+                    wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    fence_proxy_async_all();
+                }
+                if (lane == 0) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
                     mbar_wait(&empty[s], ph ^ 1u, p.status, 100, s);
@@ -233,12 +237,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                     (int32_t)(kt * kGemmBlockK), (int32_t)n0);
                     }
                 }
-            } else {
-                it += k_tiles;
+                __syncwarp();
             }
-            __syncwarp();
         }
-    } else if (warp == 1) {
+    } else if (warp == 5) {
         // ------------------------------- MMA issuer ---------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR);
@@ -289,66 +291,94 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp < 4) {
+    } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------
-        const uint32_t t = threadIdx.x - 64;  // 0..63
+        // Warp j takes the K tiles whose running index is j modulo 4.  For its K tile it loads, per
+        // lane, four A-scale words (rows lane, lane + 32, ...: exactly the 16 bytes of atom row `lane`)
+        // and for every 128 columns of B four pairs of 16-bit halves (the file layout keeps the two
+        // scales of a 64-deep K group together), and stores them as 16-byte atom rows.
+        constexpr uint32_t kNB = BLOCK_N / 32;  // B words per lane
+        const uint32_t j = warp - 6;
         const uint32_t sf_row_bytes = p.K / 32;
-        uint32_t it = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+        const uint32_t my_tiles = (num_tiles > blockIdx.x) ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+        const uint32_t total_it = my_tiles * k_tiles;
+        uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
+        uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
+        uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+
+        auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
+            const uint32_t seq = it / k_tiles;
+            const uint32_t kt = it - seq * k_tiles;
+            TileCoord tc = tile_coord(blockIdx.x + seq * gridDim.x, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
-            if (p.flags != nullptr) {
-                wait_rows_ready(p, m0, lane);
+            if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
+                gated_seq = seq;
+                gated_seg = kt / p.seg_ktiles;
+                wait_rows_ready(p, m0, lane, gated_seg);
             }
-            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % kStages;
-                const uint32_t ph = (it / kStages) & 1u;
-                // issue the global loads before waiting for the stage to drain
-                uint32_t va[2], vb[BLOCK_N / 64];
 #pragma unroll
-                for (uint32_t i = 0; i < 2; ++i) {
-                    const uint32_t row = m0 + t + i * 64;
-                    va[i] = 0x7F7F7F7Fu;
-                    if (row < p.Mg) {
-                        va[i] = __ldcg(reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u));
-                    }
+            for (uint32_t i = 0; i < 4; ++i) {
+                const uint32_t row = m0 + i * 32 + lane;
+                ra[i] = 0x7F7F7F7Fu;
+                if (row < p.Mg) {
+                    ra[i] = *reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u);
                 }
+            }
 #pragma unroll
-                for (uint32_t i = 0; i < BLOCK_N / 64; ++i) {
-                    const uint32_t n = n0 + t + i * 64;
-                    vb[i] = 0x7F7F7F7Fu;
-                    if (n < p.N) {
-                        const uint16_t lo =
-                            __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt) * p.N + n) * 2));
-                        const uint16_t hi =
-                            __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt + 1) * p.N + n) * 2));
-                        vb[i] = (uint32_t)lo | ((uint32_t)hi << 16);
-                    }
+            for (uint32_t i = 0; i < kNB; ++i) {
+                const uint32_t n = n0 + i * 32 + lane;
+                rlo[i] = 0x7F7Fu;
+                rhi[i] = 0x7F7Fu;
+                if (n < p.N) {
+                    rlo[i] = __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt) * p.N + n) * 2));
+                    rhi[i] = __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt + 1) * p.N + n) * 2));
                 }
-                mbar_wait(&empty[s], ph ^ 1u, p.status, 105, s);
-                uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
-                uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
+            }
+        };
+
+        uint32_t it = j;
+        if (it < total_it) {
+            issue_loads(it, cur_a, cur_lo, cur_hi);
+        }
+        for (; it < total_it; it += kSfWarps) {
+            const bool has_next = it + kSfWarps < total_it;
+            if (has_next) {
+                issue_loads(it + kSfWarps, nxt_a, nxt_lo, nxt_hi);
+            }
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            mbar_wait(&empty[s], ph ^ 1u, p.status, 105, s);
+            uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
+            uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
+            *reinterpret_cast<uint4*>(sfa + lane * 16u) = make_uint4(cur_a[0], cur_a[1], cur_a[2], cur_a[3]);
 #pragma unroll
-                for (uint32_t i = 0; i < 2; ++i) {
-                    const uint32_t r = t + i * 64;
-                    *reinterpret_cast<uint32_t*>(sfa + (r & 31u) * 16u + (r >> 5) * 4u) = va[i];
-                }
+            for (uint32_t h = 0; h < kNB / 4; ++h) {
+                uint4 v;
+                v.x = cur_lo[h * 4 + 0] | (cur_hi[h * 4 + 0] << 16);
+                v.y = cur_lo[h * 4 + 1] | (cur_hi[h * 4 + 1] << 16);
+                v.z = cur_lo[h * 4 + 2] | (cur_hi[h * 4 + 2] << 16);
+                v.w = cur_lo[h * 4 + 3] | (cur_hi[h * 4 + 3] << 16);
+                *reinterpret_cast<uint4*>(sfb + h * 512u + lane * 16u) = v;
+            }
+            fence_proxy_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&full_sf[s]);
+            }
+            if (has_next) {
 #pragma unroll
-                for (uint32_t i = 0; i < BLOCK_N / 64; ++i) {
-                    const uint32_t n = t + i * 64;
-                    *reinterpret_cast<uint32_t*>(sfb + (n >> 7) * 512u + (n & 31u) * 16u + ((n & 127u) >> 5) * 4u) = vb[i];
-                }
-                fence_proxy_async_shared();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full_sf[s]);
+                for (uint32_t i = 0; i < 4; ++i) cur_a[i] = nxt_a[i];
+#pragma unroll
+                for (uint32_t i = 0; i < kNB; ++i) {
+                    cur_lo[i] = nxt_lo[i];
+                    cur_hi[i] = nxt_hi[i];
                 }
             }
         }
     } else {
         // ------------------------------- epilogue -----------------------------------------
-        const uint32_t q = warp - 4;  // TMEM lane quarter == warp index modulo 4
+        const uint32_t q = warp;  // TMEM lane quarter == warp index modulo 4
         OutT* c = reinterpret_cast<OutT*>(p.c);
         constexpr uint32_t kChunks = BLOCK_N / 32;
         uint32_t ti = 0;
@@ -412,7 +442,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 5) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }

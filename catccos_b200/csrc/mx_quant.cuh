@@ -29,14 +29,15 @@ struct QuantPushParams {
     uint32_t M, K;
     uint32_t produce;         // 0: skip the producer part (the harness that runs the two parts apart)
     uint32_t publish;         // 0: nobody waits on this shard's flags (single rank, plain quantise)
+    uint32_t sys_scope;       // 1: some destination is another GPU (system-scope fences), 0: all local
     uint32_t rank, world, epoch;
     uint32_t segs_per_chunk;  // a 16-row chunk is split into this many column segments (work items)
     uint32_t seg_cols;        // columns per segment (multiple of 512)
     uint32_t num_dst;
     uint8_t* dst_codes[kMaxRanks];   // where this shard's codes [M, K] go at destination d
     uint8_t* dst_scales[kMaxRanks];  // where this shard's scales [M, K/32] go at destination d
-    uint32_t* dst_flags[kMaxRanks];  // destination d's flag words for this source (one per chunk) or nullptr
-    uint32_t* counters;              // local, one per chunk, zero between calls (segs_per_chunk > 1 only)
+    uint32_t* dst_flags[kMaxRanks];  // destination d's flag words for this source, one per (chunk, segment)
+                                     // at index chunk * segs_per_chunk + segment, or nullptr
     // consumer (standalone quantise + allgather with outputs outside symmetric memory):
     // copy the peers' shards from this GPU's stage to the caller's outputs as their flags arrive
     uint32_t consume;
@@ -110,27 +111,29 @@ __device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, uint32_t& byte)
     return o;
 }
 
-// Publishes a finished chunk: every thread's stores are ordered before the flag words.
-__device__ __forceinline__ void publish_chunk(const QuantPushParams& p, uint32_t chunk)
+// Publishing a finished work item: every thread's stores are ordered before the flag words.  The fences
+// are system-scope only when a destination is another GPU; a single-GPU run stays at GPU scope.
+__device__ __forceinline__ void publish_fence(const QuantPushParams& p)
+{
+    if (p.sys_scope) {
+        __threadfence_system();
+    } else {
+        __threadfence();
+    }
+}
+
+// One work item = one (16-row chunk, column segment), owned by exactly one CTA, which publishes it alone.
+__device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t flag_index)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        bool last = true;
-        if (p.segs_per_chunk > 1) {
-            const uint32_t old = atomicAdd(p.counters + chunk, 1u);
-            last = (old == p.segs_per_chunk - 1);
-            if (last) {
-                p.counters[chunk] = 0;
-                __threadfence_system();
-            }
-        }
-        if (last) {
+        publish_fence(p);
 #pragma unroll
-            for (uint32_t d = 0; d < (uint32_t)kMaxRanks; ++d) {
-                if (d < p.num_dst && p.dst_flags[d] != nullptr) {
-                    st_release_sys(p.dst_flags[d] + chunk, p.epoch);
-                }
+        for (uint32_t d = 0; d < (uint32_t)kMaxRanks; ++d) {
+            if (d < p.num_dst && p.dst_flags[d] != nullptr) {
+                // the fence above already ordered the data; the flag itself can be a relaxed store
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[d] + flag_index), "r"(p.epoch)
+                             : "memory");
             }
         }
     }
@@ -147,8 +150,10 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
     const bool sf_vec = (sf_cols % 4u) == 0u;
 
     for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-        const uint32_t chunk = item / p.segs_per_chunk;
-        const uint32_t seg = item - chunk * p.segs_per_chunk;
+        // segment-major: the first K segment of every row is published first, so a consumer that walks
+        // K in order can start early and follow the quantiser
+        const uint32_t seg = item / chunks;
+        const uint32_t chunk = item - seg * chunks;
         const uint32_t c_begin = seg * p.seg_cols;
         const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
         const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
@@ -215,7 +220,7 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
             }
         }
         if (p.publish) {
-            publish_chunk(p, chunk);
+            publish_item(p, chunk * p.segs_per_chunk + seg);
         }
     }
 
@@ -227,8 +232,9 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
     for (uint32_t item = blockIdx.x; item < peer_items; item += gridDim.x) {
         const uint32_t chunk = item / (p.world - 1);
         const uint32_t src = (p.rank + 1 + item % (p.world - 1)) % p.world;
-        if (threadIdx.x == 0) {
-            if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk, p.epoch, p.timeout_ns)) {
+        if (threadIdx.x < p.segs_per_chunk) {
+            const uint32_t* f = p.flags + (size_t)src * p.flag_stride + chunk * p.segs_per_chunk + threadIdx.x;
+            if (!wait_flag_ge(f, p.epoch, p.timeout_ns)) {
                 report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
             }
         }

@@ -116,7 +116,9 @@ int catccos_b200_last_status(uint32_t out[4]);
  *   "block_n"         0 = automatic, 128 or 256 = GEMM tile width
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
  *   "phase_mask"      bit 0 = launch the producer side, bit 1 = launch the consumer side (default 3);
- *                     the single-GPU harness runs all ranks' producers before any consumer. */
+ *                     the single-GPU harness runs all ranks' producers before any consumer.
+ *   "publish_scope"   0 = automatic, 1 = system-scope fences, 2 = GPU-scope fences (tuning / diagnosis)
+ *   "quant_items_per_sm" work items per SM the quantise kernel aims for (default 4) */
 int catccos_b200_set_option(const char* key, int64_t value);
 
 /* Number of kernels this library has launched since it was loaded. */
