@@ -235,6 +235,16 @@ int quant_grid(const RankCtx& rc, bool device_tiny, bool prequant)
     } else {
         fn = (const void*)mx_quant_push_kernel<false, false>;
     }
+    // An SM keeps one shared-memory carve-out for all resident CTAs.  The GEMM needs the largest one;
+    // asking for the same carve-out here lets quantise CTAs and a GEMM CTA share an SM, which is what
+    // makes the two kernels overlap instead of taking turns.
+    static bool carveout_set[3][kMaxRanks * 2] = {};
+    const int which = prequant ? 2 : (device_tiny ? 1 : 0);
+    if (rc.device < kMaxRanks * 2 && !carveout_set[which][rc.device]) {
+        cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+        carveout_set[which][rc.device] = true;
+    }
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kQuantThreads, 0) != cudaSuccess || per_sm < 1) {
         per_sm = 1;
     }
