@@ -138,6 +138,7 @@ struct State {
     int phase_mask = 3;
     int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
     int quant_items_per_sm = 4;
+    int fuse_mode = 0;       // 0 = quantise warps inside the GEMM kernel, 1 = two kernels on two streams
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
 };
@@ -224,26 +225,18 @@ bool stage_layout(size_t symm_bytes, uint32_t W, uint32_t M, uint32_t K, StageLa
 // ---------------------------------------------------------------------------------------------
 // launches
 // ---------------------------------------------------------------------------------------------
-int quant_grid(const RankCtx& rc, bool device_tiny, bool prequant)
+int quant_grid(const RankCtx& rc)
 {
     int per_sm = 0;
-    const void* fn = nullptr;
-    if (prequant) {
-        fn = (const void*)mx_quant_push_kernel<false, true>;
-    } else if (device_tiny) {
-        fn = (const void*)mx_quant_push_kernel<true, false>;
-    } else {
-        fn = (const void*)mx_quant_push_kernel<false, false>;
-    }
+    const void* fn = (const void*)mx_quant_push_kernel;
     // An SM keeps one shared-memory carve-out for all resident CTAs.  The GEMM needs the largest one;
-    // asking for the same carve-out here lets quantise CTAs and a GEMM CTA share an SM, which is what
-    // makes the two kernels overlap instead of taking turns.
-    static bool carveout_set[3][kMaxRanks * 2] = {};
-    const int which = prequant ? 2 : (device_tiny ? 1 : 0);
-    if (rc.device < kMaxRanks * 2 && !carveout_set[which][rc.device]) {
+    // asking for the same carve-out here lets quantise CTAs and a GEMM CTA share an SM when the two run
+    // as separate kernels.
+    static bool carveout_set[kMaxRanks * 2] = {};
+    if (rc.device < kMaxRanks * 2 && !carveout_set[rc.device]) {
         cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaGetLastError();
-        carveout_set[which][rc.device] = true;
+        carveout_set[rc.device] = true;
     }
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kQuantThreads, 0) != cudaSuccess || per_sm < 1) {
         per_sm = 1;
@@ -252,6 +245,16 @@ int quant_grid(const RankCtx& rc, bool device_tiny, bool prequant)
         per_sm = 6;
     }
     return per_sm * rc.num_sms;
+}
+
+uint32_t quant_mode(bool prequant)
+{
+    return prequant ? kQuantPreQuantised : (g.tiny_block_rule != 0 ? kQuantDeviceTiny : kQuantGolden);
+}
+
+uint32_t quant_sys_scope(uint32_t world)
+{
+    return g.publish_scope == 1 ? 1u : (g.publish_scope == 2 ? 0u : (world > 1 ? 1u : 0u));
 }
 
 void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
@@ -268,8 +271,7 @@ void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
 
 int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, bool produce)
 {
-    const bool dev_tiny = g.tiny_block_rule != 0;
-    int grid = quant_grid(rc, dev_tiny, prequant);
+    int grid = quant_grid(rc);
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     uint32_t items = produce ? chunks * p.segs_per_chunk : 0;
     if (p.consume) {
@@ -281,14 +283,9 @@ int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool pre
     }
     if ((uint32_t)grid > items) grid = (int)items;
     p.produce = produce ? 1u : 0u;
-    p.sys_scope = g.publish_scope == 1 ? 1u : (g.publish_scope == 2 ? 0u : (p.world > 1 ? 1u : 0u));
-    if (prequant) {
-        mx_quant_push_kernel<false, true><<<grid, kQuantThreads, 0, st>>>(p);
-    } else if (dev_tiny) {
-        mx_quant_push_kernel<true, false><<<grid, kQuantThreads, 0, st>>>(p);
-    } else {
-        mx_quant_push_kernel<false, false><<<grid, kQuantThreads, 0, st>>>(p);
-    }
+    p.mode = quant_mode(prequant);
+    p.sys_scope = quant_sys_scope(p.world);
+    mx_quant_push_kernel<<<grid, kQuantThreads, 0, st>>>(p);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -307,10 +304,10 @@ int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t o
     return 0;
 }
 
-template <uint32_t BLOCK_N, bool B_MN, typename OutT>
+template <uint32_t BLOCK_N, bool B_MN, typename OutT, bool FUSED>
 int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p)
 {
-    auto kern = mx_gemm_kernel<BLOCK_N, B_MN, OutT>;
+    auto kern = mx_gemm_kernel<BLOCK_N, B_MN, OutT, FUSED>;
     static bool attr_done[kMaxRanks * 2] = {};
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -319,13 +316,13 @@ int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUt
                                       (int)GemmSmem<BLOCK_N>::kDynamicBytes));
         attr_done[dev] = true;
     }
-    kern<<<grid, kGemmThreads, GemmSmem<BLOCK_N>::kDynamicBytes, st>>>(ta, tb, p);
+    kern<<<grid, FUSED ? kGemmFusedThreads : kGemmThreads, GemmSmem<BLOCK_N>::kDynamicBytes, st>>>(ta, tb, p);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
 }
 
-int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p)
+int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p, bool fused_quant = false)
 {
     if (!g.drv.Load()) {
         return CATCCOS_B200_ECUDA;
@@ -360,10 +357,14 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     p.status = rc.status;
     p.timeout_ns = g.timeout_ns;
     const bool f16 = g.c_dtype == 1;
-#define CATCCOS_GEMM_CASE(BN, MN)                                                             \
-    if (bn == BN && b_mn == MN) {                                                             \
-        return f16 ? launch_gemm_inst<BN, MN, __half>(grid, st, ta, tb, p)                    \
-                   : launch_gemm_inst<BN, MN, __nv_bfloat16>(grid, st, ta, tb, p);            \
+#define CATCCOS_GEMM_CASE(BN, MN)                                                                     \
+    if (bn == BN && b_mn == MN) {                                                                     \
+        if (fused_quant) {                                                                            \
+            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p)                  \
+                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p);          \
+        }                                                                                             \
+        return f16 ? launch_gemm_inst<BN, MN, __half, false>(grid, st, ta, tb, p)                     \
+                   : launch_gemm_inst<BN, MN, __nv_bfloat16, false>(grid, st, ta, tb, p);             \
     }
     CATCCOS_GEMM_CASE(256, true)
     CATCCOS_GEMM_CASE(256, false)
@@ -429,39 +430,29 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * L.stage_bytes;
     const uint32_t rank = (uint32_t)g.rank;
 
-    if (produce) {
-        QuantPushParams q = {};
-        q.in = a;
-        q.in_scales = (const uint8_t*)a_scale;
-        q.M = M;
-        q.K = K;
-        q.rank = rank;
-        q.world = W;
-        q.epoch = epoch;
-        q.num_dst = W;
-        q.publish = 1;
-        choose_segments(M, K, rc.num_sms, q);
-        for (uint32_t d = 0; d < W; ++d) {
-            uint8_t* base = sa->base[d] + stage_off;
-            q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
-            q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
-            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
-        }
-        q.status = rc.status;
-        q.timeout_ns = g.timeout_ns;
-        cudaStream_t qs = consume ? rc.side : st;
-        if (consume) {
-            CUDA_TRY(cudaEventRecord(rc.fork, st));
-            CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
-        }
-        rcode = launch_quant_push(rc, qs, q, prequant, true);
-        if (rcode != 0) return rcode;
-        if (consume) {
-            CUDA_TRY(cudaEventRecord(rc.join, rc.side));
-        }
+    QuantPushParams q = {};
+    q.in = a;
+    q.in_scales = (const uint8_t*)a_scale;
+    q.M = M;
+    q.K = K;
+    q.rank = rank;
+    q.world = W;
+    q.epoch = epoch;
+    q.num_dst = W;
+    q.publish = 1;
+    q.segs_per_chunk = seg.segs_per_chunk;
+    q.seg_cols = seg.seg_cols;
+    for (uint32_t d = 0; d < W; ++d) {
+        uint8_t* base = sa->base[d] + stage_off;
+        q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
+        q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
+        q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
     }
-    if (consume) {
-        GemmParams p = {};
+    q.status = rc.status;
+    q.timeout_ns = g.timeout_ns;
+
+    GemmParams p = {};
+    {
         uint8_t* base = sa->base[rank] + stage_off;
         p.a_scales = base + L.scales_off;
         p.b_scales = (const uint8_t*)b_scale;
@@ -477,7 +468,32 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         p.rank = rank;
         p.m_local = M;
         p.epoch = epoch;
-        rcode = launch_gemm(rc, st, base + L.codes_off, b, p);
+    }
+    const uint8_t* a_stage = sa->base[rank] + stage_off + L.codes_off;
+
+    if (produce && consume && g.fuse_mode == 0) {
+        // one launch: the quantise-and-push warps ride in the GEMM kernel
+        p.q = q;
+        p.q.produce = 1;
+        p.q.mode = quant_mode(prequant);
+        p.q.sys_scope = quant_sys_scope(W);
+        return launch_gemm(rc, st, a_stage, b, p, true);
+    }
+    if (produce) {
+        // two launches: the producer on the side stream, the GEMM on the caller's stream beside it
+        cudaStream_t qs = consume ? rc.side : st;
+        if (consume) {
+            CUDA_TRY(cudaEventRecord(rc.fork, st));
+            CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
+        }
+        rcode = launch_quant_push(rc, qs, q, prequant, true);
+        if (rcode != 0) return rcode;
+        if (consume) {
+            CUDA_TRY(cudaEventRecord(rc.join, rc.side));
+        }
+    }
+    if (consume) {
+        rcode = launch_gemm(rc, st, a_stage, b, p);
         if (rcode != 0) return rcode;
         if (produce) {
             CUDA_TRY(cudaStreamWaitEvent(st, rc.join, 0));
@@ -946,6 +962,8 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.phase_mask = (int)value;
     } else if (k == "publish_scope" && value >= 0 && value <= 2) {
         g.publish_scope = (int)value;
+    } else if (k == "fuse_mode" && (value == 0 || value == 1)) {
+        g.fuse_mode = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
         g.quant_items_per_sm = (int)value;
     } else {

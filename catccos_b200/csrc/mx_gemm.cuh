@@ -21,6 +21,11 @@
 //             bytes (the next K tile's loads are in flight while the current one is stored),
 //             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects
 //
+// With FUSED_QUANT the CTA carries eight more warps (10-17) that run the quantise-and-push producer
+// (mx_quant.cuh) on this rank's bf16 shard: quantise, store to every rank's stage over NVLink, publish
+// flags.  The GEMM warps of the same launch (and of the peers' launches) consume behind them, so the
+// quantisation, the allgather and the matmul are one kernel.
+//
 // When `flags` is set, a tile is not touched before every (source rank, 16-row chunk) under its
 // rows has been published with the current epoch by the quantise-and-push kernel; tiles are
 // visited in the order the chunks arrive (own shard first, then chunk by chunk over the peers).
@@ -31,12 +36,14 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace catccos {
 
 constexpr uint32_t kGemmBlockM = 128;
 constexpr uint32_t kGemmBlockK = 128;   // bytes == elements (8-bit codes): one 128-byte swizzle row
 constexpr uint32_t kGemmThreads = 320;
+constexpr uint32_t kGemmFusedThreads = kGemmThreads + kQuantThreads;
 constexpr uint32_t kSfWarps = 4;
 constexpr uint32_t kRowsPerChunk = 16;  // granularity of the ready flags
 constexpr uint32_t kTmemCols = 512;
@@ -54,6 +61,7 @@ struct GemmParams {
     uint32_t world, rank, m_local, epoch;
     uint64_t timeout_ns;
     StatusBlock* status;
+    QuantPushParams q;  // the producer's work when the quantise warps ride in this kernel
 };
 
 template <uint32_t BLOCK_N>
@@ -155,8 +163,8 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b)
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <uint32_t BLOCK_N, bool B_MN_MAJOR, typename OutT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <uint32_t BLOCK_N, bool B_MN_MAJOR, typename OutT, bool FUSED_QUANT>
+__global__ void __launch_bounds__(FUSED_QUANT ? kGemmFusedThreads : kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
 {
     using S = GemmSmem<BLOCK_N>;
@@ -291,6 +299,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
+    } else if (FUSED_QUANT && warp >= 10) {
+        // ------------------------------- quantise-and-push producer -----------------------
+        quant_push_producer(p.q, threadIdx.x - kGemmThreads, blockIdx.x, gridDim.x, 1);
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------
         // Warp j takes the K tiles whose running index is j modulo 4.  For its K tile it loads, per

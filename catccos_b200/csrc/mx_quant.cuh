@@ -11,7 +11,7 @@
 // Arithmetic per 32-element block (bit-exact with the reference's CPU golden, "native" rounding):
 //   E = biased exponent of the largest |x|;  scale byte = E - 8;  code = RNE_sat_E4M3(x * 2^(127 - byte)).
 //   Blocks whose largest |x| is below 1e-12 follow the golden (scale byte 0x7F, signed-zero codes) or,
-//   with kDeviceTiny, the reference device kernel (byte = max(E - 8, 0)).  Inf/NaN blocks: 0xFF / 0x7F.
+//   in mode kQuantDeviceTiny, the reference device kernel (byte = max(E - 8, 0)).  Inf/NaN blocks: 0xFF / 0x7F.
 #pragma once
 
 #include "common.cuh"
@@ -21,12 +21,16 @@ namespace catccos {
 constexpr uint32_t kQuantThreads = 256;
 constexpr uint32_t kQuantRowsPerItem = 16;  // == kRowsPerChunk of the GEMM gate: 8 warps x 2 rows
 constexpr uint32_t kQuantColsPerWarpStep = 512;
+constexpr uint32_t kQuantGolden = 0;        // tiny blocks follow the CPU golden
+constexpr uint32_t kQuantDeviceTiny = 1;    // tiny blocks follow the reference device kernel
+constexpr uint32_t kQuantPreQuantised = 2;  // input is already codes + scales: copy and publish only
 
 struct QuantPushParams {
     // producer: this rank's shard
     const void* in;           // bf16 [M, K]  (or, for the pre-quantised push, E4M3 codes [M, K])
     const uint8_t* in_scales; // pre-quantised push only: E8M0 [M, K/32]
     uint32_t M, K;
+    uint32_t mode;            // kQuantGolden / kQuantDeviceTiny / kQuantPreQuantised
     uint32_t produce;         // 0: skip the producer part (the harness that runs the two parts apart)
     uint32_t publish;         // 0: nobody waits on this shard's flags (single rank, plain quantise)
     uint32_t sys_scope;       // 1: some destination is another GPU (system-scope fences), 0: all local
@@ -73,12 +77,11 @@ __device__ __forceinline__ uint32_t encode4(uint32_t a, uint32_t b, float mul)
 }
 
 // Scale byte and multiplier for a block whose largest |bf16 bits| is amax.
-template <bool kDeviceTiny>
-__device__ __forceinline__ void block_scale(uint32_t amax, uint32_t& byte, float& mul, bool& nonfinite)
+__device__ __forceinline__ void block_scale(uint32_t amax, bool device_tiny, uint32_t& byte, float& mul, bool& nonfinite)
 {
     const uint32_t E = amax >> 7;
     nonfinite = (E == 0xFFu);
-    if (kDeviceTiny) {
+    if (device_tiny) {
         byte = E > 8u ? E - 8u : 0u;
         mul = byte == 0u ? 0.0f : __uint_as_float((254u - byte) << 23);
     } else {
@@ -92,14 +95,13 @@ __device__ __forceinline__ void block_scale(uint32_t amax, uint32_t& byte, float
 }
 
 // Quantises 16 bf16 values held by one lane (two lanes share a 32-block).
-template <bool kDeviceTiny>
-__device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, uint32_t& byte)
+__device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, bool device_tiny, uint32_t& byte)
 {
     uint32_t amax = max(absmax_bits8(v0), absmax_bits8(v1));
     amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     float mul;
     bool nonfinite;
-    block_scale<kDeviceTiny>(amax, byte, mul, nonfinite);
+    block_scale(amax, device_tiny, byte, mul, nonfinite);
     uint4 o;
     o.x = encode4(v0.x, v0.y, mul);
     o.y = encode4(v0.z, v0.w, mul);
@@ -111,23 +113,24 @@ __device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, uint32_t& byte)
     return o;
 }
 
-// Publishing a finished work item: every thread's stores are ordered before the flag words.  The fences
-// are system-scope only when a destination is another GPU; a single-GPU run stays at GPU scope.
-__device__ __forceinline__ void publish_fence(const QuantPushParams& p)
+// Barrier among the 256 threads of one quantise group (barrier 0 when the group is the whole CTA).
+__device__ __forceinline__ void quant_group_sync(uint32_t bar_id)
 {
-    if (p.sys_scope) {
-        __threadfence_system();
-    } else {
-        __threadfence();
-    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kQuantThreads) : "memory");
 }
 
-// One work item = one (16-row chunk, column segment), owned by exactly one CTA, which publishes it alone.
-__device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t flag_index)
+// Publishing a finished work item: every thread's stores are ordered before the flag words.  The fences
+// are system-scope only when a destination is another GPU; a single-GPU run stays at GPU scope.
+// One work item = one (16-row chunk, column segment), owned by exactly one group, which publishes it alone.
+__device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t flag_index, uint32_t tid, uint32_t bar_id)
 {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        publish_fence(p);
+    quant_group_sync(bar_id);
+    if (tid == 0) {
+        if (p.sys_scope) {
+            __threadfence_system();
+        } else {
+            __threadfence();
+        }
 #pragma unroll
         for (uint32_t d = 0; d < (uint32_t)kMaxRanks; ++d) {
             if (d < p.num_dst && p.dst_flags[d] != nullptr) {
@@ -139,17 +142,22 @@ __device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t 
     }
 }
 
-template <bool kDeviceTiny, bool kPreQuantised>
-__global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
+// The producer: a group of 256 threads (tid 0..255) takes work items worker, worker + num_workers, ...
+// and for each quantises (or copies) 16 rows x one column segment, stores the result at every
+// destination and publishes the item's flag.  It never waits on anybody.
+__device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, uint32_t tid, uint32_t worker,
+                                                    uint32_t num_workers, uint32_t bar_id)
 {
-    const uint32_t warp = threadIdx.x >> 5;
-    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = tid >> 5;
+    const uint32_t lane = tid & 31;
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t items = p.produce ? chunks * p.segs_per_chunk : 0u;
     const uint32_t sf_cols = p.K / 32;
     const bool sf_vec = (sf_cols % 4u) == 0u;
+    const bool prequant = p.mode == kQuantPreQuantised;
+    const bool device_tiny = p.mode == kQuantDeviceTiny;
 
-    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+    for (uint32_t item = worker; item < items; item += num_workers) {
         // segment-major: the first K segment of every row is published first, so a consumer that walks
         // K in order can start early and follow the quantiser
         const uint32_t seg = item / chunks;
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
                 const uint32_t row = row0 + r;
                 v[r][0] = v[r][1] = make_uint4(0, 0, 0, 0);
                 if (col_ok && row < p.M) {
-                    if (kPreQuantised) {
+                    if (prequant) {
                         v[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
                                                                        (size_t)row * p.K + col));
                     } else {
@@ -184,14 +192,14 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
 #pragma unroll
             for (uint32_t r = 0; r < 2; ++r) {
                 const uint32_t row = row0 + r;
-                if (kPreQuantised) {
+                if (prequant) {
                     o[r] = v[r][0];
                     byte[r] = 0;
                     if (col_ok && row < p.M && (lane & 1u) == 0u) {
                         byte[r] = p.in_scales[(size_t)row * sf_cols + col / 32];
                     }
                 } else {
-                    o[r] = quant16<kDeviceTiny>(v[r][0], v[r][1], byte[r]);
+                    o[r] = quant16(v[r][0], v[r][1], device_tiny, byte[r]);
                 }
                 // scale bytes of 8 lanes (4 blocks) packed into one word on lanes 0, 8, 16, 24
                 const uint32_t base = lane & ~7u;
@@ -220,13 +228,20 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
             }
         }
         if (p.publish) {
-            publish_item(p, chunk * p.segs_per_chunk + seg);
+            publish_item(p, chunk * p.segs_per_chunk + seg, tid, bar_id);
         }
     }
+}
+
+__global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
+{
+    quant_push_producer(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
 
     if (!p.consume) {
         return;
     }
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t sf_cols = p.K / 32;
     // ---- consumer: stage -> caller's outputs, chunk by chunk as the peers' flags arrive ----
     const uint32_t peer_items = (p.world - 1) * chunks;
     for (uint32_t item = blockIdx.x; item < peer_items; item += gridDim.x) {

@@ -117,6 +117,8 @@ int catccos_b200_last_status(uint32_t out[4]);
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
  *   "phase_mask"      bit 0 = launch the producer side, bit 1 = launch the consumer side (default 3);
  *                     the single-GPU harness runs all ranks' producers before any consumer.
+ *   "fuse_mode"       0 = the quantise-and-push warps run inside the GEMM kernel (one launch, default),
+ *                     1 = quantise kernel and GEMM kernel as two launches on two streams
  *   "publish_scope"   0 = automatic, 1 = system-scope fences, 2 = GPU-scope fences (tuning / diagnosis)
  *   "quant_items_per_sm" work items per SM the quantise kernel aims for (default 4) */
 int catccos_b200_set_option(const char* key, int64_t value);

@@ -56,6 +56,7 @@ def main():
         b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
         b_deq = mx_oracle.dequant_weight(bc, bs)
         for rnd in range(3):
+            capi.set_option("fuse_mode", 1 if rnd == 2 else 0)  # the last round runs as two kernels
             bits = [workloads.activation_bits(cfg, r, seed=rnd) for r in range(world)]
             c = torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda")
             capi.mx_quant_allgather_matmul(dev_bf16(bits[rank]), b_d, bs_d, c, symm, world)
@@ -72,6 +73,7 @@ def main():
                                              b_d, bs_d, c2, symm, world)
                 status_ok((name, "prequant"))
                 assert torch.equal(c2, c), "pre-quantised and fused paths must agree bit for bit"
+        capi.set_option("fuse_mode", 0)
         capi.symm_free(symm)
     capi.finalize()
     print(f"rank {rank} OK", flush=True)

@@ -125,10 +125,13 @@ def test_prequantised_allgather_matmul_emulated(capi, cuda, oracle, local_world,
         assert bad == 0, (r, bad, maxdiff)
 
 
-def test_fused_single_rank_two_streams(capi, cuda, oracle):
-    # world 1 through the production path: quantise kernel on the side stream, GEMM gated on its flags
+@pytest.mark.parametrize("fuse_mode", [0, 1])
+def test_fused_single_rank(capi, cuda, oracle, fuse_mode):
+    # world 1 through the production paths: quantise warps inside the GEMM kernel (0), or the quantise
+    # kernel on a side stream with the GEMM gated on its flags (1)
     torch = cuda
     capi.finalize()
+    capi.set_option("fuse_mode", fuse_mode)
     cfg = workloads.Config("t", 640, 1024, 768, (1,), "normal", "")
     a_bits = workloads.activation_bits(cfg, 0, seed=7)
     bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=7))
@@ -145,6 +148,7 @@ def test_fused_single_rank_two_streams(capi, cuda, oracle):
     bad, maxdiff = oracle.check_close(c_d.float().cpu().numpy(), gold, 1e-2, 1e-3)
     assert bad == 0, (bad, maxdiff)
     capi.symm_free(symm)
+    capi.set_option("fuse_mode", 0)
 
 
 def test_missing_peer_is_reported_not_hung(capi, cuda, local_world):
