@@ -25,6 +25,7 @@ EXPORTS = [
     "catccos_b200_mx_quant_allgather_matmul",
     "catccos_b200_mx_quant",
     "catccos_b200_mx_gemm",
+    "catccos_b200_mx_quant_matmul_static",
     "catccos_b200_transpose_weight",
     "catccos_b200_last_status",
     "catccos_b200_set_option",
@@ -78,6 +79,7 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_mx_quant_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_gemm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
+    L.catccos_b200_mx_quant_matmul_static.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_transpose_weight.argtypes = [vp, vp, vp, u32, u32]
     L.catccos_b200_last_status.argtypes = [ctypes.POINTER(u32)]
     L.catccos_b200_set_option.argtypes = [ctypes.c_char_p, i64]
@@ -183,6 +185,15 @@ def mx_gemm(a_codes, a_scales, b, b_scales, out=None, out_dtype=None):
            load().catccos_b200_mx_gemm(_stream(), a_codes.data_ptr(), a_scales.data_ptr(), b.data_ptr(),
                                        b_scales.data_ptr(), out.data_ptr(), m, n, k))
     return out
+
+
+def mx_quant_matmul_static(a_bf16, b, b_scales, c) -> None:
+    """The allocation-free single-GPU fused call (scratch is the library's built-in device array)."""
+    m, k = a_bf16.shape
+    n = b_scales.shape[1]
+    _check("catccos_b200_mx_quant_matmul_static",
+           load().catccos_b200_mx_quant_matmul_static(_stream(), a_bf16.data_ptr(), b.data_ptr(), b_scales.data_ptr(),
+                                                      c.data_ptr(), m, n, k))
 
 
 def transpose_weight(b):

@@ -976,3 +976,121 @@ int catccos_b200_set_option(const char* key, int64_t value)
 uint64_t catccos_b200_launch_count(void) { return g_launches.load(); }
 
 }  // extern "C"
+
+// =============================================================================================
+// Allocation-free single-GPU entry point
+// =============================================================================================
+namespace {
+
+// Scratch of catccos_b200_mx_quant_matmul_static: the quantised copy of A and its ready flags live in
+// this file-scope device array instead of a buffer from catccos_b200_symm_alloc.  Every GPU that
+// loads the library carries it (about 8.3 MiB) until the process exits.
+constexpr size_t kStaticMaxElems = size_t(8) << 20;  // m * k may not exceed this
+constexpr uint32_t kStaticMaxFlags = 8192;           // (16-row chunks) x (K segments) may not exceed this
+constexpr size_t kStaticFlagsOff = 0;
+constexpr size_t kStaticStatusOff = kStaticMaxFlags * sizeof(uint32_t);
+constexpr size_t kStaticScalesOff = kStaticStatusOff + 1024;
+constexpr size_t kStaticCodesOff = kStaticScalesOff + kStaticMaxElems / 32;
+constexpr size_t kStaticBytes = kStaticCodesOff + kStaticMaxElems;
+static_assert(kStaticScalesOff % 256 == 0 && kStaticCodesOff % 1024 == 0, "TMA and vector stores need these aligned");
+
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticBytes];
+
+struct StaticDeviceState {
+    uint8_t* ptr = nullptr;  // device address of g_static_scratch on this device
+    int num_sms = 0;
+    uint32_t epoch = 0;
+};
+StaticDeviceState g_static_dev[kMaxRanks * 2];
+std::mutex g_static_mu;
+
+}  // namespace
+
+extern "C" int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_bf16, const void* b, const void* b_scale,
+                                                   void* c, uint32_t m, uint32_t n, uint32_t k)
+{
+    if (!a_bf16 || !b || !b_scale || !c || m == 0 || n == 0 || k == 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    if (k % kGemmBlockK != 0 || n % 16 != 0) {
+        ERROR_LOG("mx_quant_matmul_static: k must be a multiple of 128 and n of 16 (got n=%u k=%u)", n, k);
+        return CATCCOS_B200_EINVAL;
+    }
+    if ((size_t)m * k > kStaticMaxElems) {
+        ERROR_LOG("mx_quant_matmul_static: m * k = %zu exceeds the built-in scratch of %zu elements; "
+                  "use catccos_b200_mx_quant_allgather_matmul with a buffer from catccos_b200_symm_alloc",
+                  (size_t)m * k, kStaticMaxElems);
+        return CATCCOS_B200_ENOMEM;
+    }
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxRanks * 2) {
+        return CATCCOS_B200_EINVAL;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDeviceState& sd = g_static_dev[dev];
+    if (sd.ptr == nullptr) {
+        // One-time set-up for this device (it is current).  In host code the array's name is only a
+        // stand-in; the address a kernel may use comes from the runtime.
+        void* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        CUDA_TRY(cudaDeviceGetAttribute(&sd.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        if (!g.drv.Load()) {
+            return CATCCOS_B200_ECUDA;
+        }
+        sd.ptr = static_cast<uint8_t*>(p);
+    }
+    RankCtx rc;  // a view for the launcher: nothing is created or owned here
+    rc.device = dev;
+    rc.num_sms = sd.num_sms;
+    rc.status = reinterpret_cast<StatusBlock*>(sd.ptr + kStaticStatusOff);
+
+    QuantPushParams seg = {};
+    choose_segments(m, k, rc.num_sms, seg);
+    const uint32_t chunks = (m + kRowsPerChunk - 1) / kRowsPerChunk;
+    if ((size_t)chunks * seg.segs_per_chunk > kStaticMaxFlags) {
+        ERROR_LOG("mx_quant_matmul_static: %u row chunks x %u K segments exceed the built-in %u flag words", chunks,
+                  seg.segs_per_chunk, kStaticMaxFlags);
+        return CATCCOS_B200_ENOMEM;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    // the array keeps what the last call left: the flag words are epochs that only grow, so stale ones
+    // never satisfy this call; the status record must start at zero
+    CUDA_TRY(cudaMemsetAsync(rc.status, 0, sizeof(StatusBlock), st));
+    const uint32_t epoch = ++sd.epoch;
+
+    GemmParams p = {};
+    p.a_scales = sd.ptr + kStaticScalesOff;
+    p.b_scales = (const uint8_t*)b_scale;
+    p.c = c;
+    p.Mg = m;
+    p.N = n;
+    p.K = k;
+    p.flags = reinterpret_cast<const uint32_t*>(sd.ptr + kStaticFlagsOff);
+    p.flag_stride = kStaticMaxFlags;
+    p.segs = seg.segs_per_chunk;
+    p.seg_ktiles = seg.seg_cols / kGemmBlockK;
+    p.world = 1;
+    p.rank = 0;
+    p.m_local = m;
+    p.epoch = epoch;
+    QuantPushParams& q = p.q;
+    q.in = a_bf16;
+    q.M = m;
+    q.K = k;
+    q.world = 1;
+    q.epoch = epoch;
+    q.num_dst = 1;
+    q.publish = 1;
+    q.produce = 1;
+    q.mode = quant_mode(false);
+    q.sys_scope = 0;
+    q.segs_per_chunk = seg.segs_per_chunk;
+    q.seg_cols = seg.seg_cols;
+    q.dst_codes[0] = sd.ptr + kStaticCodesOff;
+    q.dst_scales[0] = sd.ptr + kStaticScalesOff;
+    q.dst_flags[0] = reinterpret_cast<uint32_t*>(sd.ptr + kStaticFlagsOff);
+    q.status = rc.status;
+    q.timeout_ns = g.timeout_ns;
+    return launch_gemm(rc, st, sd.ptr + kStaticCodesOff, b, p, true);
+}

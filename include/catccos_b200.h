@@ -99,6 +99,29 @@ int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint
 int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,
                          uint32_t m, uint32_t n, uint32_t k);
 
+/* Fused quantise + matmul on one GPU that allocates nothing.  It has no counterpart in the reference.
+ * c [m, n] = dequant(quantise(a_bf16 [m, k])) x dequant(b [k, n], b_scale [k/64, n, 2]): the same two
+ * fused stages as catccos_b200_mx_quant_allgather_matmul at rankSize 1, but the quantised copy of A and
+ * its ready flags live in an array that is part of the library image (a file-scope __device__ array of
+ * about 8.3 MiB that every GPU loading the library holds until the process exits) instead of a buffer
+ * from catccos_b200_symm_alloc.
+ *
+ * It is meant for callers that must not allocate device memory where the call is made: code that runs
+ * inside a region whose memory was planned ahead of time (an inference server that reserved all of HBM
+ * for its own pools at start-up, so a late cudaMalloc fails or fragments them), and latency-critical
+ * loops where an allocation would serialise the device.  The call itself makes no cudaMalloc, cudaFree
+ * or other allocating call; inputs and the output are the caller's.
+ *
+ * Limits: m * k <= 8 Mi elements (8 388 608) and at most 8192 (16-row chunk, K segment) pairs, else
+ * CATCCOS_B200_ENOMEM with an [ERROR] line; k % 128 == 0, n % 16 == 0.  The first call on each device
+ * looks up the array's device address (that device must be current) and should therefore be made
+ * before any stream capture begins.  All calls on a device share the one array, which keeps the last
+ * call's contents: calls are correct back to back on one stream, but two calls whose kernels overlap
+ * on the GPU (different streams, no dependency) race on it.  Device-side wait records of this path
+ * are not readable through catccos_b200_last_status. */
+int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_bf16, const void* b, const void* b_scale, void* c,
+                                        uint32_t m, uint32_t n, uint32_t k);
+
 /* Transposed copy of a weight, b [k, n] -> bt [n, k], for option "b_layout" = 1.  No reference
  * counterpart: the reference reads B through CATLASS layout tags (mx_allgather_matmul.hpp:148-151). */
 int catccos_b200_transpose_weight(void* stream, const void* b, void* bt, uint32_t k, uint32_t n);
