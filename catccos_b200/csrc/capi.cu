@@ -16,6 +16,7 @@
 #include "bootstrap.hpp"
 #include "common.cuh"
 #include "mx_gemm.cuh"
+#include "mx_gemm_pair.cuh"
 #include "mx_quant.cuh"
 
 using namespace catccos;
@@ -138,6 +139,7 @@ struct State {
     int phase_mask = 3;
     int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
     int quant_items_per_sm = 4;
+    int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
     int fuse_mode = 0;       // 0 = quantise warps inside the GEMM kernel, 1 = two kernels on two streams
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
@@ -322,6 +324,51 @@ int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUt
     return 0;
 }
 
+template <typename OutT, bool FUSED>
+int launch_gemm_pair_inst(int max_pairs_hint, uint32_t tiles, cudaStream_t st, const CUtensorMap& ta,
+                          const CUtensorMap& tb, const GemmParams& p)
+{
+    auto kern = mx_gemm_pair_kernel<OutT, FUSED>;
+    const int threads = FUSED ? kGemmFusedThreads : kGemmThreads;
+    static bool attr_done[kMaxRanks * 2] = {};
+    static int max_clusters[kMaxRanks * 2] = {};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < kMaxRanks * 2 && !attr_done[dev]) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairSmem::kDynamicBytes));
+        // how many pairs can be resident at once: the grid never exceeds it, because CTAs of one launch wait
+        // on flags that the quantise warps of other CTAs of the same launch publish
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * max_pairs_hint);
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = PairSmem::kDynamicBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = max_pairs_hint;
+        }
+        max_clusters[dev] = n;
+        attr_done[dev] = true;
+    }
+    uint32_t pairs = (uint32_t)(dev < kMaxRanks * 2 ? max_clusters[dev] : max_pairs_hint);
+    if (pairs > (uint32_t)max_pairs_hint) pairs = (uint32_t)max_pairs_hint;
+    if (pairs > tiles) pairs = tiles;
+    kern<<<2 * pairs, threads, PairSmem::kDynamicBytes, st>>>(ta, tb, p);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// Rough K-tile periods (microseconds) measured on B200 for the three tilings; used only to pick one.
+constexpr double kPeriodPair256 = 0.53, kPeriodSingle256 = 0.53, kPeriodSingle128 = 0.40;
+
 int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p, bool fused_quant = false)
 {
     if (!g.drv.Load()) {
@@ -331,18 +378,42 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         ERROR_LOG("mx gemm needs K %% 128 == 0 and N %% 16 == 0 (got M=%u N=%u K=%u)", p.Mg, p.N, p.K);
         return CATCCOS_B200_EINVAL;
     }
-    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)p.c) & 15u || ((uintptr_t)p.a_scales & 3u) ||
+    if ((((uintptr_t)a | (uintptr_t)b) & 15u) || ((uintptr_t)p.c & 31u) || ((uintptr_t)p.a_scales & 3u) ||
         ((uintptr_t)p.b_scales & 1u)) {
-        ERROR_LOG("mx gemm operands must be 16-byte aligned");
+        ERROR_LOG("mx gemm operands must be 16-byte aligned (the output 32-byte aligned)");
         return CATCCOS_B200_EINVAL;
     }
+    const bool b_mn = g.b_layout == 0;
+    const bool f16 = g.c_dtype == 1;
+    p.status = rc.status;
+    p.timeout_ns = g.timeout_ns;
+    // tiling choice: waves x K-tile period of each candidate (same K for all, so K drops out)
+    const uint32_t m128 = (p.Mg + 127) / 128, m256 = (p.Mg + 255) / 256;
+    const uint32_t n128 = (p.N + 127) / 128, n256 = (p.N + 255) / 256;
+    const uint32_t sms = (uint32_t)rc.num_sms, max_pairs = sms / 2;
+    auto waves = [](uint32_t tiles, uint32_t slots) { return (double)((tiles + slots - 1) / slots); };
+    const double t_pair = waves(m256 * n256, max_pairs) * kPeriodPair256;
+    const double t_256 = waves(m128 * n256, sms) * kPeriodSingle256;
+    const double t_128 = waves(m128 * n128, sms) * kPeriodSingle128;
+    bool use_pair = b_mn && (g.cta_pair == 1 || (g.cta_pair == 0 && g.block_n == 0 && t_pair < t_256 && t_pair < t_128));
     uint32_t bn = (uint32_t)g.block_n;
     if (bn != 128 && bn != 256) {
-        // 256-wide tiles halve the A traffic per FLOP; take them when they still give every SM a tile
-        const uint32_t tiles256 = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + 255) / 256);
-        bn = (p.N > 128 && tiles256 >= (uint32_t)rc.num_sms) ? 256 : 128;
+        bn = (p.N > 128 && t_256 <= t_128) ? 256 : 128;
     }
-    const bool b_mn = g.b_layout == 0;
+    if (use_pair) {
+        CUtensorMap pa, pb;
+        int rc2 = encode_map_2d(&pa, a, p.K, p.Mg, kGemmBlockK, 128);
+        if (rc2 != 0) return rc2;
+        rc2 = encode_map_2d(&pb, b, p.N, p.K, 128, kGemmBlockK);
+        if (rc2 != 0) return rc2;
+        const uint32_t tiles = m256 * n256;
+        if (fused_quant) {
+            return f16 ? launch_gemm_pair_inst<__half, true>((int)max_pairs, tiles, st, pa, pb, p)
+                       : launch_gemm_pair_inst<__nv_bfloat16, true>((int)max_pairs, tiles, st, pa, pb, p);
+        }
+        return f16 ? launch_gemm_pair_inst<__half, false>((int)max_pairs, tiles, st, pa, pb, p)
+                   : launch_gemm_pair_inst<__nv_bfloat16, false>((int)max_pairs, tiles, st, pa, pb, p);
+    }
     CUtensorMap ta, tb;
     int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM);
     if (rcode != 0) return rcode;
@@ -354,9 +425,6 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     if (rcode != 0) return rcode;
     const uint32_t tiles = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + bn - 1) / bn);
     int grid = (int)(tiles < (uint32_t)rc.num_sms ? tiles : (uint32_t)rc.num_sms);
-    p.status = rc.status;
-    p.timeout_ns = g.timeout_ns;
-    const bool f16 = g.c_dtype == 1;
 #define CATCCOS_GEMM_CASE(BN, MN)                                                                     \
     if (bn == BN && b_mn == MN) {                                                                     \
         if (fused_quant) {                                                                            \
@@ -962,6 +1030,8 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.phase_mask = (int)value;
     } else if (k == "publish_scope" && value >= 0 && value <= 2) {
         g.publish_scope = (int)value;
+    } else if (k == "cta_pair" && value >= 0 && value <= 2) {
+        g.cta_pair = (int)value;
     } else if (k == "fuse_mode" && (value == 0 || value == 1)) {
         g.fuse_mode = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {

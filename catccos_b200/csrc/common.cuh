@@ -38,6 +38,14 @@ __device__ __forceinline__ void report_status(StatusBlock* st, uint32_t code, ui
     }
 }
 
+// 32-byte store (one full sector); the address must be 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8])
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns()
 {
     uint64_t t;
@@ -269,6 +277,40 @@ __device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint
         : "memory");
 }
 
+// The same instructions taking the 64-bit descriptors as (low, high) halves: the issuing thread keeps the
+// constant high halves in registers and only adds to the low half (the start address), which keeps its
+// instruction count per K tile small - the tensor pipe queues only a couple of MMAs ahead, so a slow
+// issuing thread starves it.
+__device__ __forceinline__ void umma_mxf8_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                               uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %5, [%7], [%8], p;\n\t"
+        "}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(tmem_sfa),
+          "r"(tmem_sfb)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_cp_sf_lohi(uint32_t tmem_dst, uint32_t lo, uint32_t hi)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 d;\n\t"
+        "mov.b64 d, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t"
+        "}"
+        ::"r"(tmem_dst), "r"(lo), "r"(hi)
+        : "memory");
+}
+
 // Copies one 512-byte scale-factor atom (32 rows x 16 bytes) from shared memory into four
 // tensor-memory columns, replicated over the four 32-lane groups.
 __device__ __forceinline__ void tcgen05_cp_sf(uint32_t tmem_dst, uint64_t smem_desc)
@@ -294,6 +336,166 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+}  // namespace catccos
+
+// ------------------------------------------------------------------------------------------
+// CTA pairs (clusters of two, tcgen05 cta_group::2)
+// ------------------------------------------------------------------------------------------
+namespace catccos {
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cluster address of the location that `local_smem_addr` names in CTA `cta_rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t cta_rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait on a barrier that the other CTA of the pair arrives on.  What these barriers guard moves
+// through the async proxies (TMA, tcgen05), so the default CTA-scope acquire is what is needed; a
+// cluster-scope acquire on every poll costs several hundred nanoseconds.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id,
+                                                  uint32_t stage)
+{
+    if (mbar_try_wait_cluster(bar, parity)) {
+        return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 0xFFu) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
+            report_status(st, kStatusBarrierTimeout, id, stage, parity);
+            return false;
+        }
+    }
+    return true;
+}
+
+// TMA tile load issued by either CTA of a pair; the completion bytes are credited to the barrier at
+// `bar_cluster_addr`, which may live in the other CTA.  No multicast: every CTA loads its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int32_t x,
+                                                 int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// Arrives on the barrier at the same shared-memory offset in every CTA of cta_mask once all tcgen05
+// operations issued so far by this thread have completed.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(cta_mask)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_mxf8_pair_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                    uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %5, [%7], [%8], p;\n\t"
+        "}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(tmem_sfa),
+          "r"(tmem_sfb)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_cp_sf_pair_lohi(uint32_t tmem_dst, uint32_t lo, uint32_t hi)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 d;\n\t"
+        "mov.b64 d, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t"
+        "}"
+        ::"r"(tmem_dst), "r"(lo), "r"(hi)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_cp_sf_pair(uint32_t tmem_dst, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
 }
 
 }  // namespace catccos

@@ -77,17 +77,19 @@ struct GemmSmem {
     static constexpr uint32_t kOffSfa = kOffB + kStages * kBBytes;
     static constexpr uint32_t kOffSfb = kOffSfa + kStages * kSfaBytes;
     static constexpr uint32_t kOffBar = kOffSfb + kStages * kSfbBytes;
-    // barriers: full_ab[S], full_sf[S], empty[S], tmem_full[2], tmem_empty[2], overlap_free[2]
-    static constexpr uint32_t kNumBars = 3 * kStages + 6;
+    // barriers: full[S] (TMA bytes + one scale-loader arrival), empty[S], tmem_full[2], tmem_empty[2],
+    // overlap_free[2]
+    static constexpr uint32_t kNumBars = 2 * kStages + 6;
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack to align the base to 1024 bytes
     // accumulator placement in tensor memory: two 128 x BLOCK_N fp32 accumulators.  For
-    // BLOCK_N = 256 they overlap by 16 columns (240..255) so that 16 columns stay free for the
+    // BLOCK_N = 256 they overlap by 24 columns (232..255) so that 24 columns stay free for two sets of
     // scale factors; the epilogue drains the shared columns first and then lets the next tile start.
     static constexpr bool kOverlap = (BLOCK_N == 256);
-    static constexpr uint32_t kAccCol1 = kOverlap ? 240 : 256;
-    static constexpr uint32_t kSfCol = kOverlap ? 496 : 480;  // SFA: 4 columns, SFB: 4 per 128 columns of N
+    static constexpr uint32_t kAccCol1 = kOverlap ? 232 : 256;
+    static constexpr uint32_t kSfCol = 488;       // two scale-factor sets (even / odd K tile), 12 columns each:
+    static constexpr uint32_t kSfSetCols = 12;    // SFA 4 columns, then SFB 4 per 128 columns of N
 };
 
 struct TileCoord {
@@ -174,10 +176,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kOffBar);
-    uint64_t* full_ab = bars;
-    uint64_t* full_sf = bars + kStages;
-    uint64_t* empty = bars + 2 * kStages;
-    uint64_t* tmem_full = bars + 3 * kStages;
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kStages;
+    uint64_t* tmem_full = bars + 2 * kStages;
     uint64_t* tmem_empty = tmem_full + 2;
     uint64_t* overlap_free = tmem_empty + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
@@ -192,8 +193,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(&full_ab[s], 1);
-            mbar_init(&full_sf[s], 1);
+            mbar_init(&full[s], 2);  // the producer's expect_tx arrival and one scale-loader warp
             mbar_init(&empty[s], 1);
         }
         for (uint32_t a = 0; a < 2; ++a) {
@@ -230,18 +230,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
                     mbar_wait(&empty[s], ph ^ 1u, p.status, 100, s);
-                    mbar_arrive_expect_tx(&full_ab[s], S::kABytes + S::kBBytes);
-                    tma_load_2d(smem + S::kOffA + s * S::kABytes, &tmap_a, &full_ab[s], (int32_t)(kt * kGemmBlockK),
+                    mbar_arrive_expect_tx(&full[s], S::kABytes + S::kBBytes);
+                    tma_load_2d(smem + S::kOffA + s * S::kABytes, &tmap_a, &full[s], (int32_t)(kt * kGemmBlockK),
                                 (int32_t)m0);
                     if constexpr (B_MN_MAJOR) {
                         // [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
                         for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
-                            tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full_ab[s],
+                            tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full[s],
                                         (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
                         }
                     } else {
                         // transposed copy [N, K]: box = 128 (K, contiguous) x BLOCK_N rows
-                        tma_load_2d(smem + S::kOffB + s * S::kBBytes, &tmap_b, &full_ab[s],
+                        tma_load_2d(smem + S::kOffB + s * S::kBBytes, &tmap_b, &full[s],
                                     (int32_t)(kt * kGemmBlockK), (int32_t)n0);
                     }
                 }
@@ -250,13 +250,55 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else if (warp == 5) {
         // ------------------------------- MMA issuer ---------------------------------------
+        // The tensor pipe accepts only a couple of MMAs ahead of the one it is executing, so whatever
+        // this thread does between the last MMA of a K tile and the first of the next is idle time for
+        // the pipe.  The loop therefore looks one K tile ahead: after the first two MMAs of a K tile
+        // are queued it waits for the next stage and copies its scale atoms (into the other of two
+        // scale-factor sets in tensor memory), and only then queues the last two MMAs.
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR);
-            const uint32_t sfa_col = tmem_base + S::kSfCol;
-            const uint32_t sfb_col = tmem_base + S::kSfCol + 4;
-            uint32_t it = 0;
-            uint32_t ti = 0;
-            for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
+            const uint32_t my_tiles = (num_tiles > blockIdx.x) ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+            const uint32_t total_it = my_tiles * k_tiles;
+
+            // descriptor halves: the high words are constants, the low words are start addresses >> 4
+            const uint32_t hi_ab = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
+            const uint32_t hi_b_mn = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
+            const uint32_t lo_ab_lbo = (uint32_t)make_smem_desc(0, 16, 1024, 2);         // LBO field of A / K-major B
+            const uint32_t lo_b_mn_lbo = (uint32_t)make_smem_desc(0, 16384, 1024, 2);    // LBO field of MN-major B
+            const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
+            const uint32_t a_lo0 = lo_ab_lbo | (smem_u32(smem + S::kOffA) >> 4);
+            const uint32_t b_lo0 = (B_MN_MAJOR ? lo_b_mn_lbo : lo_ab_lbo) | (smem_u32(smem + S::kOffB) >> 4);
+            const uint32_t b_hi = B_MN_MAJOR ? hi_b_mn : hi_ab;
+            const uint32_t sfa_lo0 = smem_u32(smem + S::kOffSfa) >> 4;
+            const uint32_t sfb_lo0 = smem_u32(smem + S::kOffSfb) >> 4;
+            constexpr uint32_t kKbStepA = 32u >> 4;                                  // 32 bytes along K
+            constexpr uint32_t kKbStepB = (B_MN_MAJOR ? 4096u : 32u) >> 4;          // 32 K rows of 128 bytes, or 32 bytes
+            const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
+
+            auto stage_ready = [&](uint32_t it, uint32_t s, uint32_t ph) {  // wait for K tile `it` (stage s), copy its scale atoms
+                mbar_wait(&full[s], ph, p.status, 103, s);
+                tcgen05_fence_after();
+                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                // 32 rows x 16 bytes per atom, no swizzle, 8-row groups 128 bytes apart
+                tcgen05_cp_sf_lohi(sf, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
+#pragma unroll
+                for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
+                    tcgen05_cp_sf_lohi(sf + 4 + 4 * h, sfb_lo0 + s * (S::kSfbBytes >> 4) + h * (512u >> 4), hi_sf);
+                }
+            };
+            // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; K advances 32 bytes in the row.
+            // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart, 8-row K groups
+            // 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO); or K-major like A.
+            auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
+                umma_mxf8_lohi(d_col, a_lo + kb * kKbStepA, hi_ab, b_lo + kb * kKbStepB, b_hi, idesc_with_sf_id(idesc, kb), sf,
+                               sf + 4, accumulate);
+            };
+
+            if (total_it > 0) {
+                stage_ready(0, 0, 0);
+            }
+            uint32_t it = 0, s = 0, ph = 0;
+            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
                 const uint32_t acc = ti & 1u;
                 const uint32_t acc_ph = (ti >> 1) & 1u;
                 const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
@@ -266,34 +308,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 tcgen05_fence_after();
                 for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
-                    mbar_wait(&full_sf[s], ph, p.status, 103, s);
-                    mbar_wait(&full_ab[s], ph, p.status, 104, s);
-                    tcgen05_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + S::kOffA + s * S::kABytes);
-                    const uint32_t b_addr = smem_u32(smem + S::kOffB + s * S::kBBytes);
-                    // scale atoms -> tensor memory (32 rows x 16 bytes each, no swizzle, 8-row groups 128 bytes apart)
-                    tcgen05_cp_sf(sfa_col, make_smem_desc(smem_u32(smem + S::kOffSfa + s * S::kSfaBytes), 0, 128, 0));
-                    for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
-                        tcgen05_cp_sf(sfb_col + 4 * h,
-                                      make_smem_desc(smem_u32(smem + S::kOffSfb + s * S::kSfbBytes + h * 512u), 0, 128, 0));
+                    const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
+                    const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
+                    const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                    const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
+                    const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
+                    if (it + 1 < total_it) {
+                        stage_ready(it + 1, s_next, ph_next);
                     }
-#pragma unroll
-                    for (uint32_t kb = 0; kb < kGemmBlockK / 32; ++kb) {
-                        // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; K advances 32 bytes in the row
-                        const uint64_t da = make_smem_desc(a_addr + kb * 32u, 16, 1024, 2);
-                        uint64_t db;
-                        if constexpr (B_MN_MAJOR) {
-                            // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart,
-                            // 8-row K groups 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO)
-                            db = make_smem_desc(b_addr + kb * 4096u, 16384, 1024, 2);
-                        } else {
-                            db = make_smem_desc(b_addr + kb * 32u, 16, 1024, 2);
-                        }
-                        umma_mxf8(d_col, da, db, idesc_with_sf_id(idesc, kb), sfa_col, sfb_col, (kt | kb) != 0u);
-                    }
+                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
                     tcgen05_commit(&empty[s]);
+                    s = s_next;
+                    ph = ph_next;
                 }
                 tcgen05_commit(&tmem_full[acc]);
             }
@@ -375,7 +404,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             fence_proxy_async_shared();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&full_sf[s]);
+                mbar_arrive(&full[s]);
             }
             if (has_next) {
 #pragma unroll
@@ -425,13 +454,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     OutT* dst = c + (size_t)row * p.N + col;
                     if (col + 32u <= p.N) {
 #pragma unroll
-                        for (uint32_t v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2<OutT>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                            o.y = pack2<OutT>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                            o.z = pack2<OutT>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                            o.w = pack2<OutT>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                            *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                        for (uint32_t v = 0; v < 2; ++v) {
+                            uint32_t o[8];
+#pragma unroll
+                            for (uint32_t e = 0; e < 8; ++e) {
+                                o[e] = pack2<OutT>(__uint_as_float(r[v * 16 + 2 * e]), __uint_as_float(r[v * 16 + 2 * e + 1]));
+                            }
+                            st_global_v8(dst + v * 16, o);  // one full 32-byte sector per store
                         }
                     } else {
 #pragma unroll

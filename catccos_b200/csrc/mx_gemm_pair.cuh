@@ -1,0 +1,367 @@
+// MXFP8 block-scaled GEMM on CTA pairs (clusters of two SMs, tcgen05 cta_group::2).
+//
+// Same operator, operands, layouts and flag gating as mx_gemm.cuh; what changes is the tile: a pair of
+// CTAs owns a 256 x 256 output tile.  CTA r of the pair loads A rows [m0 + 128 r, +128) and B columns
+// [n0 + 128 r, +128) of every K tile (32 KB per K tile per SM instead of 48 KB), the leader CTA (r = 0)
+// issues one tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 32) that reads both CTAs' shared memory, and
+// each CTA ends up with the accumulator of its own 128 rows x 256 columns in its own tensor memory.
+// Every CTA loads its own tiles with plain TMA (no cluster multicast anywhere); what crosses the pair is
+// only barrier traffic:
+//   full[s]                     lives in the leader; both CTAs' TMA bytes and scale-loader arrivals go there
+//   empty[s], tmem_full[a]      live in each CTA; the leader's tcgen05.commit arrives on both copies
+//   tmem_empty[a], overlap_free[a]  live in the leader; the epilogue warps of both CTAs arrive there
+#pragma once
+
+#include "mx_gemm.cuh"
+
+namespace catccos {
+
+constexpr uint32_t kPairBlockM = 256;
+constexpr uint32_t kPairBlockN = 256;
+
+struct PairSmem {
+    static constexpr uint32_t kStages = 6;
+    static constexpr uint32_t kABytes = 128 * kGemmBlockK;  // this CTA's 128 rows
+    static constexpr uint32_t kBBytes = 128 * kGemmBlockK;  // this CTA's 128 columns
+    static constexpr uint32_t kSfaBytes = 512;
+    static constexpr uint32_t kSfbBytes = 1024;  // all 256 columns: each CTA multiplies by the whole N tile
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kOffA + kStages * kABytes;
+    static constexpr uint32_t kOffSfa = kOffB + kStages * kBBytes;
+    static constexpr uint32_t kOffSfb = kOffSfa + kStages * kSfaBytes;
+    static constexpr uint32_t kOffBar = kOffSfb + kStages * kSfbBytes;
+    static constexpr uint32_t kNumBars = 2 * kStages + 6;
+    static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr uint32_t kBytes = kOffTmemPtr + 16;
+    static constexpr uint32_t kDynamicBytes = kBytes + 1024;
+    static constexpr uint32_t kAccCol1 = 232;  // the two accumulators share columns 232..255 (see mx_gemm.cuh)
+    static constexpr uint32_t kSfCol = 488;    // two scale-factor sets of 12 columns (even / odd K tile)
+    static constexpr uint32_t kSfSetCols = 12;
+};
+
+// Tile order for pairs: as tile_coord, with 256-row tiles.
+__device__ __forceinline__ TileCoord pair_tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
+{
+    uint32_t mo = idx / n_tiles;
+    TileCoord t;
+    t.n_tile = idx - mo * n_tiles;
+    t.m_tile = mo;
+    if (p.flags != nullptr && p.world > 1) {
+        if (p.m_local % kPairBlockM == 0) {
+            const uint32_t tps = p.m_local / kPairBlockM;
+            if (mo < tps) {
+                t.m_tile = p.rank * tps + mo;
+            } else {
+                const uint32_t j = mo - tps;
+                const uint32_t mt = j / (p.world - 1);
+                const uint32_t src = (p.rank + 1 + j % (p.world - 1)) % p.world;
+                t.m_tile = src * tps + mt;
+            }
+        } else {
+            t.m_tile = (mo + (p.rank * p.m_local) / kPairBlockM) % m_tiles;
+        }
+    }
+    return t;
+}
+
+template <typename OutT, bool FUSED_QUANT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED_QUANT ? kGemmFusedThreads : kGemmThreads, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
+{
+    using S = PairSmem;
+    constexpr uint32_t kStages = S::kStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kOffBar);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kStages;
+    uint64_t* tmem_full = bars + 2 * kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint64_t* overlap_free = tmem_empty + 2;
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();  // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+
+    const uint32_t m_tiles = (p.Mg + kPairBlockM - 1) / kPairBlockM;
+    const uint32_t n_tiles = (p.N + kPairBlockN - 1) / kPairBlockN;
+    const uint32_t num_tiles = m_tiles * n_tiles;
+    const uint32_t k_tiles = p.K / kGemmBlockK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 4);  // per CTA: the producer's expect_tx arrival and one scale-loader warp
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 8);    // four epilogue warps in each CTA
+            mbar_init(&overlap_free[a], 8);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 5) {
+        tmem_alloc_pair(tmem_ptr_smem, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anybody arrives on the other's
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 4) {
+        // ------------------------------- TMA producer (both CTAs) -------------------------
+        uint32_t it = 0;
+        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs) {
+            TileCoord tc = pair_tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
+            const uint32_t n0 = tc.n_tile * kPairBlockN + cta * 128u;
+            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                if (p.flags != nullptr && kt % p.seg_ktiles == 0) {
+                    wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    fence_proxy_async_all();
+                }
+                if (lane == 0) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    mbar_wait_cluster(&empty[s], ph ^ 1u, p.status, 200, s);
+                    const uint32_t leader_bar = map_to_cta(smem_u32(&full[s]), 0);
+                    mbar_arrive_expect_tx_cluster(leader_bar, S::kABytes + S::kBBytes);
+                    tma_load_2d_pair(smem + S::kOffA + s * S::kABytes, &tmap_a, leader_bar, (int32_t)(kt * kGemmBlockK),
+                                     (int32_t)m0);
+                    tma_load_2d_pair(smem + S::kOffB + s * S::kBBytes, &tmap_b, leader_bar, (int32_t)n0,
+                                     (int32_t)(kt * kGemmBlockK));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------- MMA issuer (leader CTA only) ---------------------
+        // Same look-ahead as the single-CTA kernel: the next stage is awaited and its scale atoms copied
+        // between the second and third MMA of the current K tile.
+        if (cta == 0 && lane == 0) {
+            constexpr uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, true);
+            const uint32_t my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
+            const uint32_t total_it = my_tiles * k_tiles;
+
+            const uint32_t hi_a = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
+            const uint32_t hi_b = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
+            const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
+            const uint32_t a_lo0 = (uint32_t)make_smem_desc(0, 16, 1024, 2) | (smem_u32(smem + S::kOffA) >> 4);
+            // each CTA holds 128 columns of B (one 128-byte swizzle row per K): MN-major
+            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
+            const uint32_t sfa_lo0 = smem_u32(smem + S::kOffSfa) >> 4;
+            const uint32_t sfb_lo0 = smem_u32(smem + S::kOffSfb) >> 4;
+            const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
+
+            auto stage_ready = [&](uint32_t it, uint32_t s, uint32_t ph) {
+                mbar_wait_cluster(&full[s], ph, p.status, 203, s);
+                tcgen05_fence_after();
+                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                tcgen05_cp_sf_pair_lohi(sf, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
+                tcgen05_cp_sf_pair_lohi(sf + 4, sfb_lo0 + s * (S::kSfbBytes >> 4), hi_sf);
+                tcgen05_cp_sf_pair_lohi(sf + 8, sfb_lo0 + s * (S::kSfbBytes >> 4) + (512u >> 4), hi_sf);
+            };
+            auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
+                umma_mxf8_pair_lohi(d_col, a_lo + kb * (32u >> 4), hi_a, b_lo + kb * (4096u >> 4), hi_b,
+                                    idesc_with_sf_id(idesc, kb), sf, sf + 4, accumulate);
+            };
+
+            if (total_it > 0) {
+                stage_ready(0, 0, 0);
+            }
+            uint32_t it = 0, s = 0, ph = 0;
+            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
+                const uint32_t acc = ti & 1u;
+                const uint32_t acc_ph = (ti >> 1) & 1u;
+                const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
+                mbar_wait_cluster(&tmem_empty[acc], acc_ph ^ 1u, p.status, 201, acc);
+                if (ti > 0) {
+                    mbar_wait_cluster(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 202, acc);
+                }
+                tcgen05_fence_after();
+                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
+                    const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
+                    const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                    const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
+                    const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
+                    if (it + 1 < total_it) {
+                        stage_ready(it + 1, s_next, ph_next);
+                    }
+                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
+                    tcgen05_commit_pair(&empty[s], 3);
+                    s = s_next;
+                    ph = ph_next;
+                }
+                tcgen05_commit_pair(&tmem_full[acc], 3);
+            }
+        }
+        __syncwarp();
+    } else if (FUSED_QUANT && warp >= 10) {
+        // ------------------------------- quantise-and-push producer -----------------------
+        quant_push_producer(p.q, threadIdx.x - kGemmThreads, blockIdx.x, gridDim.x, 1);
+    } else if (warp >= 6) {
+        // ------------------------------- scale loaders (both CTAs) ------------------------
+        // A scales of this CTA's 128 rows; B scales of all 256 columns of the pair's tile.
+        constexpr uint32_t kNB = kPairBlockN / 32;
+        const uint32_t j = warp - 6;
+        const uint32_t sf_row_bytes = p.K / 32;
+        const uint32_t my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
+        const uint32_t total_it = my_tiles * k_tiles;
+        uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
+        uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
+        uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+
+        auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
+            const uint32_t seq = it / k_tiles;
+            const uint32_t kt = it - seq * k_tiles;
+            TileCoord tc = pair_tile_coord(pair + seq * num_pairs, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
+            const uint32_t n0 = tc.n_tile * kPairBlockN;
+            if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
+                gated_seq = seq;
+                gated_seg = kt / p.seg_ktiles;
+                wait_rows_ready(p, m0, lane, gated_seg);
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                const uint32_t row = m0 + i * 32 + lane;
+                ra[i] = 0x7F7F7F7Fu;
+                if (row < p.Mg) {
+                    ra[i] = *reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u);
+                }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < kNB; ++i) {
+                const uint32_t n = n0 + i * 32 + lane;
+                rlo[i] = 0x7F7Fu;
+                rhi[i] = 0x7F7Fu;
+                if (n < p.N) {
+                    rlo[i] = __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt) * p.N + n) * 2));
+                    rhi[i] = __ldg(reinterpret_cast<const uint16_t*>(p.b_scales + ((size_t)(2 * kt + 1) * p.N + n) * 2));
+                }
+            }
+        };
+
+        uint32_t it = j;
+        if (it < total_it) {
+            issue_loads(it, cur_a, cur_lo, cur_hi);
+        }
+        for (; it < total_it; it += kSfWarps) {
+            const bool has_next = it + kSfWarps < total_it;
+            if (has_next) {
+                issue_loads(it + kSfWarps, nxt_a, nxt_lo, nxt_hi);
+            }
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            mbar_wait_cluster(&empty[s], ph ^ 1u, p.status, 205, s);
+            uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
+            uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
+            *reinterpret_cast<uint4*>(sfa + lane * 16u) = make_uint4(cur_a[0], cur_a[1], cur_a[2], cur_a[3]);
+#pragma unroll
+            for (uint32_t h = 0; h < kNB / 4; ++h) {
+                uint4 v;
+                v.x = cur_lo[h * 4 + 0] | (cur_hi[h * 4 + 0] << 16);
+                v.y = cur_lo[h * 4 + 1] | (cur_hi[h * 4 + 1] << 16);
+                v.z = cur_lo[h * 4 + 2] | (cur_hi[h * 4 + 2] << 16);
+                v.w = cur_lo[h * 4 + 3] | (cur_hi[h * 4 + 3] << 16);
+                *reinterpret_cast<uint4*>(sfb + h * 512u + lane * 16u) = v;
+            }
+            fence_proxy_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(map_to_cta(smem_u32(&full[s]), 0));
+            }
+            if (has_next) {
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) cur_a[i] = nxt_a[i];
+#pragma unroll
+                for (uint32_t i = 0; i < kNB; ++i) {
+                    cur_lo[i] = nxt_lo[i];
+                    cur_hi[i] = nxt_hi[i];
+                }
+            }
+        }
+    } else {
+        // ------------------------------- epilogue (both CTAs, own 128 rows) ---------------
+        const uint32_t q = warp;
+        OutT* c = reinterpret_cast<OutT*>(p.c);
+        constexpr uint32_t kChunks = kPairBlockN / 32;
+        uint32_t ti = 0;
+        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++ti) {
+            TileCoord tc = pair_tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
+            const uint32_t n0 = tc.n_tile * kPairBlockN;
+            const uint32_t acc = ti & 1u;
+            const uint32_t acc_ph = (ti >> 1) & 1u;
+            const uint32_t d_col = acc ? S::kAccCol1 : 0u;
+            mbar_wait_cluster(&tmem_full[acc], acc_ph, p.status, 206, acc);
+            tcgen05_fence_after();
+            const uint32_t row = m0 + q * 32 + lane;
+            for (uint32_t ci = 0; ci < kChunks; ++ci) {
+                uint32_t chunk = ci;
+                if (acc == 0) {
+                    chunk = (ci == 0) ? (kChunks - 1) : ci - 1;  // the shared columns first
+                }
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + d_col + chunk * 32u, r);
+                tmem_ld_wait();
+                if (ci == 0) {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive_cluster(map_to_cta(smem_u32(&overlap_free[acc]), 0));
+                    }
+                }
+                const uint32_t col = n0 + chunk * 32u;
+                if (row < p.Mg && col < p.N) {
+                    OutT* dst = c + (size_t)row * p.N + col;
+                    if (col + 32u <= p.N) {
+#pragma unroll
+                        for (uint32_t v = 0; v < 2; ++v) {
+                            uint32_t o[8];
+#pragma unroll
+                            for (uint32_t e = 0; e < 8; ++e) {
+                                o[e] = pack2<OutT>(__uint_as_float(r[v * 16 + 2 * e]), __uint_as_float(r[v * 16 + 2 * e + 1]));
+                            }
+                            st_global_v8(dst + v * 16, o);  // one full 32-byte sector per store
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t jj = 0; jj < 32u; ++jj) {
+                            if (col + jj < p.N) {
+                                dst[jj] = static_cast<OutT>(__uint_as_float(r[jj]));
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // nobody leaves while the other CTA may still arrive on its barriers
+    if (warp == 5) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace catccos

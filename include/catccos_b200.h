@@ -140,6 +140,8 @@ int catccos_b200_last_status(uint32_t out[4]);
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
  *   "phase_mask"      bit 0 = launch the producer side, bit 1 = launch the consumer side (default 3);
  *                     the single-GPU harness runs all ranks' producers before any consumer.
+ *   "cta_pair"        0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2),
+ *                     2 = never
  *   "fuse_mode"       0 = the quantise-and-push warps run inside the GEMM kernel (one launch, default),
  *                     1 = quantise kernel and GEMM kernel as two launches on two streams
  *   "publish_scope"   0 = automatic, 1 = system-scope fences, 2 = GPU-scope fences (tuning / diagnosis)

@@ -24,6 +24,7 @@ def local_world(capi, cuda):
     yield _make
     capi.set_option("phase_mask", 3)
     capi.set_option("timeout_ms", 2000)
+    capi.set_option("cta_pair", 0)
     capi.finalize()
 
 
@@ -84,10 +85,12 @@ def _agmm_round(capi, torch, call, world):
         assert code == 0, (r, st)
 
 
+@pytest.mark.parametrize("cta_pair", [2, 1])
 @pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272)])
-def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n):
+def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n, cta_pair):
     torch = cuda
     local_world(world)
+    capi.set_option("cta_pair", cta_pair)
     t = capi.make_tiling(m, k, n, world)
     symm = _alloc_symm(capi, world, capi.symm_bytes_needed(t, False))
     cfg = workloads.Config("t", m, k, n, (world,), "normal", "")
@@ -125,13 +128,15 @@ def test_prequantised_allgather_matmul_emulated(capi, cuda, oracle, local_world,
         assert bad == 0, (r, bad, maxdiff)
 
 
+@pytest.mark.parametrize("cta_pair", [2, 1])
 @pytest.mark.parametrize("fuse_mode", [0, 1])
-def test_fused_single_rank(capi, cuda, oracle, fuse_mode):
+def test_fused_single_rank(capi, cuda, oracle, fuse_mode, cta_pair):
     # world 1 through the production paths: quantise warps inside the GEMM kernel (0), or the quantise
     # kernel on a side stream with the GEMM gated on its flags (1)
     torch = cuda
     capi.finalize()
     capi.set_option("fuse_mode", fuse_mode)
+    capi.set_option("cta_pair", cta_pair)
     cfg = workloads.Config("t", 640, 1024, 768, (1,), "normal", "")
     a_bits = workloads.activation_bits(cfg, 0, seed=7)
     bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=7))
@@ -149,6 +154,7 @@ def test_fused_single_rank(capi, cuda, oracle, fuse_mode):
     assert bad == 0, (bad, maxdiff)
     capi.symm_free(symm)
     capi.set_option("fuse_mode", 0)
+    capi.set_option("cta_pair", 0)
 
 
 def test_missing_peer_is_reported_not_hung(capi, cuda, local_world):

@@ -24,7 +24,8 @@ def _rand_problem(oracle, m, n, k, seed, a_scale=1.0, dist="normal"):
     return ac, asc, bc, bsc
 
 
-def _run(capi, torch, ac, asc, bc, bsc, block_n=0, b_layout=0, f16=False):
+def _run(capi, torch, ac, asc, bc, bsc, block_n=0, b_layout=0, f16=False, cta_pair=2):
+    capi.set_option("cta_pair", cta_pair)
     capi.set_option("block_n", block_n)
     capi.set_option("b_layout", b_layout)
     capi.set_option("c_dtype", 1 if f16 else 0)
@@ -38,6 +39,7 @@ def _run(capi, torch, ac, asc, bc, bsc, block_n=0, b_layout=0, f16=False):
         assert code == 0, st
         return out.float().cpu().numpy()
     finally:
+        capi.set_option("cta_pair", 0)
         capi.set_option("block_n", 0)
         capi.set_option("b_layout", 0)
         capi.set_option("c_dtype", 0)
@@ -138,3 +140,40 @@ def test_linearity_in_scales_at_full_size(capi, cuda, oracle):
     rows = np.r_[0:32, 500:532, 992:1024]
     gold = oracle.allgather_matmul([ac], [asc], bc, bsc, rows=rows)
     _check(oracle, c1.float().cpu().numpy()[rows], gold, k)
+
+
+# ---- CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) ----------------------------------------------
+
+def test_pair_single_tile_unit_scales(capi, cuda, oracle):
+    rng = np.random.default_rng(21)
+    m, n, k = 256, 256, 128
+    ac = rng.integers(0x30, 0x48, (m, k)).astype(np.uint8) | (rng.integers(0, 2, (m, k)).astype(np.uint8) << 7)
+    bc = rng.integers(0x30, 0x48, (k, n)).astype(np.uint8) | (rng.integers(0, 2, (k, n)).astype(np.uint8) << 7)
+    asc = np.full((m, k // 32), 0x7F, np.uint8)
+    bsc = np.full((k // 64, n, 2), 0x7F, np.uint8)
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    out = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=1)
+    _check(oracle, out, gold, k)
+
+
+def test_pair_scale_factor_routing(capi, cuda, oracle):
+    rng = np.random.default_rng(22)
+    m, n, k = 512, 512, 512
+    ac = rng.integers(0x30, 0x48, (m, k)).astype(np.uint8)
+    bc = rng.integers(0x30, 0x48, (k, n)).astype(np.uint8)
+    asc = (120 + (np.arange(m)[:, None] * 7 + np.arange(k // 32)[None, :] * 3) % 13).astype(np.uint8)
+    bs_kn = (118 + (np.arange(k // 32)[:, None] * 5 + np.arange(n)[None, :]) % 11).astype(np.uint8)
+    bsc = np.ascontiguousarray(bs_kn.reshape(k // 64, 2, n).transpose(0, 2, 1))
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    out = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=1)
+    _check(oracle, out, gold, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 1024), (100, 272, 384), (385, 2304, 7168), (3072, 2048, 256), (130, 3456, 5120)])
+def test_pair_shapes(capi, cuda, oracle, m, n, k):
+    ac, asc, bc, bsc = _rand_problem(oracle, m, n, k, seed=m + n + k + 1)
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    out = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=1)
+    _check(oracle, out, gold, k)
+    out16 = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=1, f16=True)
+    assert oracle.check_reference_rule(out16, gold, k, bf16=False)[0] == 0
