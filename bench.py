@@ -207,6 +207,9 @@ def run_gpu(args) -> None:
     else:
         capi.init(0, 1, local_rank, None)
     dev = torch.device("cuda", local_rank)
+    for kv in args.opt:
+        key, val = kv.split("=", 1)
+        capi.set_option(key, int(val))
 
     def barrier():
         if world > 1:
@@ -351,6 +354,7 @@ def run_gpu(args) -> None:
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": float(ms_e2e.mean()),
                 "h2d_bytes_per_step": int(a_host.numel() * 2), "d2h_bytes_per_step": int(c_host.numel() * 2)},
         "gpu_launches": int(launches),
+        "options": list(args.opt),
         "clocks": clocks,
         **extras,
     }
@@ -370,6 +374,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
+                    help="library option for catccos_b200_set_option (tuning runs), e.g. --opt push_mode=1")
     ap.add_argument("--lean", action="store_true",
                     help="headline loop only: no quant-allgather / unfused extras, no CPU baseline (profiling runs)")
     args = ap.parse_args()

@@ -140,6 +140,7 @@ struct State {
     int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
     int quant_items_per_sm = 4;
     int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
+    int push_mode = 0;       // fused kernel: 0 = pusher warps forward the local stage, 1 = quantise warps store to all ranks
     int fuse_mode = 0;       // 0 = quantise warps inside the GEMM kernel, 1 = two kernels on two streams
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
@@ -540,11 +541,39 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     const uint8_t* a_stage = sa->base[rank] + stage_off + L.codes_off;
 
     if (produce && consume && g.fuse_mode == 0) {
-        // one launch: the quantise-and-push warps ride in the GEMM kernel
+        // one launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
+        // warps of all ranks consume behind them
         p.q = q;
         p.q.produce = 1;
         p.q.mode = quant_mode(prequant);
-        p.q.sys_scope = quant_sys_scope(W);
+        if (g.push_mode == 1) {
+            p.q.sys_scope = quant_sys_scope(W);
+            return launch_gemm(rc, st, a_stage, b, p, true);
+        }
+        p.q.sys_scope = 0;
+        PushParams& ps = p.push;
+        ps.src_codes = q.dst_codes[rank];
+        ps.src_scales = q.dst_scales[rank];
+        ps.src_flags = q.dst_flags[rank];
+        for (uint32_t d = 0; d < W; ++d) {
+            ps.dst_codes[d] = d == rank ? nullptr : q.dst_codes[d];
+            ps.dst_scales[d] = d == rank ? nullptr : q.dst_scales[d];
+            ps.dst_flags[d] = d == rank ? nullptr : q.dst_flags[d];
+            if (d != rank) {
+                p.q.dst_codes[d] = nullptr;  // the quantise warps write the local stage only
+                p.q.dst_scales[d] = nullptr;
+                p.q.dst_flags[d] = nullptr;
+            }
+        }
+        ps.M = M;
+        ps.K = K;
+        ps.rank = rank;
+        ps.world = W;
+        ps.epoch = epoch;
+        ps.segs_per_chunk = seg.segs_per_chunk;
+        ps.seg_cols = seg.seg_cols;
+        ps.timeout_ns = g.timeout_ns;
+        ps.status = rc.status;
         return launch_gemm(rc, st, a_stage, b, p, true);
     }
     if (produce) {
@@ -1032,6 +1061,8 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.publish_scope = (int)value;
     } else if (k == "cta_pair" && value >= 0 && value <= 2) {
         g.cta_pair = (int)value;
+    } else if (k == "push_mode" && (value == 0 || value == 1)) {
+        g.push_mode = (int)value;
     } else if (k == "fuse_mode" && (value == 0 || value == 1)) {
         g.fuse_mode = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {

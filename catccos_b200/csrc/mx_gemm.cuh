@@ -21,7 +21,7 @@
 //             bytes (the next K tile's loads are in flight while the current one is stored),
 //             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects
 //
-// With FUSED_QUANT the CTA carries eight more warps (10-17) that run the quantise-and-push producer
+// With FUSED_QUANT the CTA carries ten more warps (10-19): two pusher warps, and eight that run the quantise-and-push producer
 // (mx_quant.cuh) on this rank's bf16 shard: quantise, store to every rank's stage over NVLink, publish
 // flags.  The GEMM warps of the same launch (and of the peers' launches) consume behind them, so the
 // quantisation, the allgather and the matmul are one kernel.
@@ -43,7 +43,7 @@ namespace catccos {
 constexpr uint32_t kGemmBlockM = 128;
 constexpr uint32_t kGemmBlockK = 128;   // bytes == elements (8-bit codes): one 128-byte swizzle row
 constexpr uint32_t kGemmThreads = 320;
-constexpr uint32_t kGemmFusedThreads = kGemmThreads + kQuantThreads;
+constexpr uint32_t kGemmFusedThreads = kGemmThreads + kQuantThreads + 64;  // eight producer warps + two idle ones
 constexpr uint32_t kSfWarps = 4;
 constexpr uint32_t kRowsPerChunk = 16;  // granularity of the ready flags
 constexpr uint32_t kTmemCols = 512;
@@ -61,7 +61,8 @@ struct GemmParams {
     uint32_t world, rank, m_local, epoch;
     uint64_t timeout_ns;
     StatusBlock* status;
-    QuantPushParams q;  // the producer's work when the quantise warps ride in this kernel
+    QuantPushParams q;  // the producer's work when the quantise warps ride in this kernel (local stage only)
+    PushParams push;    // the pusher warps' work: local stage -> the peers' stages
 };
 
 template <uint32_t BLOCK_N>
@@ -330,7 +331,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         __syncwarp();
     } else if (FUSED_QUANT && warp >= 10) {
         // ------------------------------- quantise-and-push producer -----------------------
-        quant_push_producer(p.q, threadIdx.x - kGemmThreads, blockIdx.x, gridDim.x, 1);
+        // Eight of the ten extra warps quantise this rank's shard into the local stage.  The two that
+        // share a scheduler (warp id modulo 4) with the MMA issuer must not compete with that single
+        // thread for issue slots; they run the pusher, a copy loop that issues an instruction only every
+        // few hundred cycles, and send the finished items on to the peers.
+        if ((warp & 3u) != (5u & 3u)) {
+            const uint32_t qw = warp - 10u - (warp > 13u ? 1u : 0u) - (warp > 17u ? 1u : 0u);  // 0..7
+            quant_push_producer(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
+        } else {
+            push_worker(p.push, lane, blockIdx.x * 2u + (warp > 13u ? 1u : 0u), gridDim.x * 2u);
+        }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------
         // Warp j takes the K tiles whose running index is j modulo 4.  For its K tile it loads, per

@@ -210,7 +210,16 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         __syncwarp();
     } else if (FUSED_QUANT && warp >= 10) {
         // ------------------------------- quantise-and-push producer -----------------------
-        quant_push_producer(p.q, threadIdx.x - kGemmThreads, blockIdx.x, gridDim.x, 1);
+        // Eight of the ten extra warps quantise this rank's shard into the local stage.  The two that
+        // share a scheduler (warp id modulo 4) with the MMA issuer must not compete with that single
+        // thread for issue slots; they run the pusher, a copy loop that issues an instruction only every
+        // few hundred cycles, and send the finished items on to the peers.
+        if ((warp & 3u) != (5u & 3u)) {
+            const uint32_t qw = warp - 10u - (warp > 13u ? 1u : 0u) - (warp > 17u ? 1u : 0u);  // 0..7
+            quant_push_producer(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
+        } else {
+            push_worker(p.push, lane, blockIdx.x * 2u + (warp > 13u ? 1u : 0u), gridDim.x * 2u);
+        }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders (both CTAs) ------------------------
         // A scales of this CTA's 128 rows; B scales of all 256 columns of the pair's tile.

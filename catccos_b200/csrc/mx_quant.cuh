@@ -233,6 +233,97 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
     }
 }
 
+// What a pusher warp needs: where this rank's quantised shard lives locally and where it goes.
+struct PushParams {
+    const uint8_t* src_codes;   // this rank's shard in its own stage: codes [M, K]
+    const uint8_t* src_scales;  //                                      scales [M, K/32]
+    const uint32_t* src_flags;  // this GPU's flag words for its own shard (published by the quantise warps)
+    uint8_t* dst_codes[kMaxRanks];   // the same shard's place in rank d's stage (nullptr for d == rank)
+    uint8_t* dst_scales[kMaxRanks];
+    uint32_t* dst_flags[kMaxRanks];  // rank d's flag words for this source
+    uint32_t M, K, rank, world, epoch;
+    uint32_t segs_per_chunk, seg_cols;
+    uint64_t timeout_ns;
+    StatusBlock* status;
+};
+
+// The pusher: one warp copies finished work items of this rank's shard from the local stage to the peers.
+// A unit of work is (work item, destination); pusher `worker` of `num_workers` takes units worker,
+// worker + num_workers, ... in item order, so early K segments leave first.  It waits (bounded) for the
+// quantise warps' local flag, copies 16 rows x one K segment with several 16-byte loads in flight,
+// fences at system scope and sets the destination's flag.  A plain copy loop like this keeps NVLink
+// busy with one or two warps per SM, which the quantise warps (stalled on HBM loads most of the time)
+// cannot do.
+__device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, uint32_t worker, uint32_t num_workers)
+{
+    if (p.world < 2) {
+        return;
+    }
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t items = chunks * p.segs_per_chunk;
+    const uint32_t peers = p.world - 1;
+    const uint32_t units = items * peers;
+    const uint32_t sf_cols = p.K / 32;
+    for (uint32_t u = worker; u < units; u += num_workers) {
+        const uint32_t item = u / peers;
+        const uint32_t d = (p.rank + 1 + (u - item * peers)) % p.world;
+        const uint32_t seg = item / chunks;
+        const uint32_t chunk = item - seg * chunks;
+        const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
+        if (lane == 0 && !wait_flag_ge(p.src_flags + flag_index, p.epoch, p.timeout_ns)) {
+            report_status(p.status, kStatusFlagTimeout, p.rank, chunk, p.epoch);
+        }
+        __syncwarp();
+        const uint32_t c_begin = seg * p.seg_cols;
+        const uint32_t cols = min(p.K, c_begin + p.seg_cols) - c_begin;
+        const uint32_t r_begin = chunk * kQuantRowsPerItem;
+        const uint32_t rows = min(p.M, r_begin + kQuantRowsPerItem) - r_begin;
+        // codes: rows x cols bytes, 16 bytes per lane per step, four steps in flight
+        const uint32_t per_row = cols / 16;
+        const uint32_t n16 = rows * per_row;
+        for (uint32_t i = lane; i < n16; i += 128) {
+            uint4 v[4];
+            size_t off[4];
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t e = i + j * 32;
+                const uint32_t r = e / per_row;
+                off[j] = (size_t)(r_begin + r) * p.K + c_begin + (size_t)(e - r * per_row) * 16;
+                if (e < n16) {
+                    v[j] = __ldcg(reinterpret_cast<const uint4*>(p.src_codes + off[j]));
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                if (i + j * 32 < n16) {
+                    *reinterpret_cast<uint4*>(p.dst_codes[d] + off[j]) = v[j];
+                }
+            }
+        }
+        // scales: rows x cols/32 bytes
+        const uint32_t sf_per_row = cols / 32;
+        if ((sf_per_row % 4u) == 0u && (sf_cols % 4u) == 0u) {
+            const uint32_t w_per_row = sf_per_row / 4;
+            for (uint32_t e = lane; e < rows * w_per_row; e += 32) {
+                const uint32_t r = e / w_per_row;
+                const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (size_t)(e - r * w_per_row) * 4;
+                *reinterpret_cast<uint32_t*>(p.dst_scales[d] + off) = __ldcg(reinterpret_cast<const uint32_t*>(p.src_scales + off));
+            }
+        } else {
+            for (uint32_t e = lane; e < rows * sf_per_row; e += 32) {
+                const uint32_t r = e / sf_per_row;
+                const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (e - r * sf_per_row);
+                p.dst_scales[d][off] = __ldcg(p.src_scales + off);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_system();
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[d] + flag_index), "r"(p.epoch) : "memory");
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
 {
     quant_push_producer(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
