@@ -140,6 +140,7 @@ struct State {
     int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
     int quant_items_per_sm = 4;
     int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
+    int group_rows = 0;      // 0 = automatic; else rows per send group (multiple of 16)
     int push_mode = 0;       // fused kernel: 0 = pusher warps forward the local stage, 1 = quantise warps store to all ranks
     int fuse_mode = 0;       // 0 = quantise warps inside the GEMM kernel, 1 = two kernels on two streams
     uint64_t timeout_ns = 2000ull * 1000000ull;
@@ -511,6 +512,13 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     q.publish = 1;
     q.segs_per_chunk = seg.segs_per_chunk;
     q.seg_cols = seg.seg_cols;
+    {
+        // A GEMM with more tiles than SMs runs in waves: send complete 256-row groups one after another so
+        // that the first wave's rows are whole early.  A single-wave GEMM starts every tile at once and is
+        // better served by one group (segment-major over all rows).
+        const uint32_t tiles = ((W * M + 127) / 128) * ((N + 255) / 256);
+        q.group_chunks = tiles > (uint32_t)rc.num_sms ? (g.group_rows > 0 ? (uint32_t)g.group_rows / kRowsPerChunk : 16u) : 0u;
+    }
     for (uint32_t d = 0; d < W; ++d) {
         uint8_t* base = sa->base[d] + stage_off;
         q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
@@ -572,9 +580,23 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         ps.epoch = epoch;
         ps.segs_per_chunk = seg.segs_per_chunk;
         ps.seg_cols = seg.seg_cols;
+        ps.group_chunks = q.group_chunks;
         ps.timeout_ns = g.timeout_ns;
         ps.status = rc.status;
         return launch_gemm(rc, st, a_stage, b, p, true);
+    }
+    if (produce && consume && g.fuse_mode == 2) {
+        // two launches, GEMM first: its CTAs take the SMs (one each, with the large shared-memory carve-out)
+        // and wait on flags; the producer's CTAs need no shared memory and are scheduled beside them
+        CUDA_TRY(cudaEventRecord(rc.fork, st));
+        CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
+        rcode = launch_gemm(rc, st, a_stage, b, p);
+        if (rcode != 0) return rcode;
+        rcode = launch_quant_push(rc, rc.side, q, prequant, true);
+        if (rcode != 0) return rcode;
+        CUDA_TRY(cudaEventRecord(rc.join, rc.side));
+        CUDA_TRY(cudaStreamWaitEvent(st, rc.join, 0));
+        return 0;
     }
     if (produce) {
         // two launches: the producer on the side stream, the GEMM on the caller's stream beside it
@@ -1061,9 +1083,11 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.publish_scope = (int)value;
     } else if (k == "cta_pair" && value >= 0 && value <= 2) {
         g.cta_pair = (int)value;
+    } else if (k == "group_rows" && value >= 0 && value <= 65536 && value % 16 == 0) {
+        g.group_rows = (int)value;
     } else if (k == "push_mode" && (value == 0 || value == 1)) {
         g.push_mode = (int)value;
-    } else if (k == "fuse_mode" && (value == 0 || value == 1)) {
+    } else if (k == "fuse_mode" && value >= 0 && value <= 2) {
         g.fuse_mode = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
         g.quant_items_per_sm = (int)value;

@@ -21,7 +21,7 @@
 //             bytes (the next K tile's loads are in flight while the current one is stored),
 //             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects
 //
-// With FUSED_QUANT the CTA carries ten more warps (10-19): two pusher warps, and eight that run the quantise-and-push producer
+// With FUSED_QUANT the CTA carries fourteen more warps (10-23): six pusher warps, and eight that run the quantise-and-push producer
 // (mx_quant.cuh) on this rank's bf16 shard: quantise, store to every rank's stage over NVLink, publish
 // flags.  The GEMM warps of the same launch (and of the peers' launches) consume behind them, so the
 // quantisation, the allgather and the matmul are one kernel.
@@ -43,7 +43,8 @@ namespace catccos {
 constexpr uint32_t kGemmBlockM = 128;
 constexpr uint32_t kGemmBlockK = 128;   // bytes == elements (8-bit codes): one 128-byte swizzle row
 constexpr uint32_t kGemmThreads = 320;
-constexpr uint32_t kGemmFusedThreads = kGemmThreads + kQuantThreads + 64;  // eight producer warps + two idle ones
+constexpr uint32_t kPushWarps = 6;
+constexpr uint32_t kGemmFusedThreads = kGemmThreads + kQuantThreads + kPushWarps * 32;  // + eight quantise warps + six pushers
 constexpr uint32_t kSfWarps = 4;
 constexpr uint32_t kRowsPerChunk = 16;  // granularity of the ready flags
 constexpr uint32_t kTmemCols = 512;
@@ -276,12 +277,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             constexpr uint32_t kKbStepB = (B_MN_MAJOR ? 4096u : 32u) >> 4;          // 32 K rows of 128 bytes, or 32 bytes
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
 
-            auto stage_ready = [&](uint32_t it, uint32_t s, uint32_t ph) {  // wait for K tile `it` (stage s), copy its scale atoms
+            // Getting K tile `it` (stage s) ready is split in three small steps that are slotted between the
+            // MMAs of the previous K tile, so that no gap between two MMA issues exceeds one MMA's run time.
+            auto stage_wait = [&](uint32_t s, uint32_t ph) {
                 mbar_wait(&full[s], ph, p.status, 103, s);
                 tcgen05_fence_after();
-                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+            };
+            auto stage_copy_sfa = [&](uint32_t it, uint32_t s) {
                 // 32 rows x 16 bytes per atom, no swizzle, 8-row groups 128 bytes apart
-                tcgen05_cp_sf_lohi(sf, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
+                tcgen05_cp_sf_lohi(sf_tmem0 + (it & 1u) * S::kSfSetCols, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
+            };
+            auto stage_copy_sfb = [&](uint32_t it, uint32_t s) {
+                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
 #pragma unroll
                 for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
                     tcgen05_cp_sf_lohi(sf + 4 + 4 * h, sfb_lo0 + s * (S::kSfbBytes >> 4) + h * (512u >> 4), hi_sf);
@@ -296,7 +303,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             };
 
             if (total_it > 0) {
-                stage_ready(0, 0, 0);
+                stage_wait(0, 0);
+                stage_copy_sfa(0, 0);
+                stage_copy_sfb(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
             for (uint32_t ti = 0; ti < my_tiles; ++ti) {
@@ -314,12 +323,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
                     const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
                     const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
+                    const bool more = it + 1 < total_it;
                     issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    if (more) {
+                        stage_wait(s_next, ph_next);
+                    }
                     issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
-                    if (it + 1 < total_it) {
-                        stage_ready(it + 1, s_next, ph_next);
+                    if (more) {
+                        stage_copy_sfa(it + 1, s_next);
                     }
                     issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    if (more) {
+                        stage_copy_sfb(it + 1, s_next);
+                    }
                     issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
                     tcgen05_commit(&empty[s]);
                     s = s_next;
@@ -331,15 +347,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         __syncwarp();
     } else if (FUSED_QUANT && warp >= 10) {
         // ------------------------------- quantise-and-push producer -----------------------
-        // Eight of the ten extra warps quantise this rank's shard into the local stage.  The two that
-        // share a scheduler (warp id modulo 4) with the MMA issuer must not compete with that single
-        // thread for issue slots; they run the pusher, a copy loop that issues an instruction only every
-        // few hundred cycles, and send the finished items on to the peers.
-        if ((warp & 3u) != (5u & 3u)) {
+        // Of the fourteen extra warps, eight quantise this rank's shard into the local stage (warps 10-19
+        // except 13 and 17, which share a scheduler with the MMA issuer and must not compete with that
+        // single thread for issue slots).  The other six (13, 17, 20-23) run the pusher, a copy loop that
+        // issues an instruction only every few hundred cycles, and send finished items on to the peers.
+        if (warp < 20u && (warp & 3u) != (5u & 3u)) {
             const uint32_t qw = warp - 10u - (warp > 13u ? 1u : 0u) - (warp > 17u ? 1u : 0u);  // 0..7
-            quant_push_producer(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
+            quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
-            push_worker(p.push, lane, blockIdx.x * 2u + (warp > 13u ? 1u : 0u), gridDim.x * 2u);
+            const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
+            push_worker(p.push, lane, blockIdx.x * kPushWarps + pw, gridDim.x * kPushWarps);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------

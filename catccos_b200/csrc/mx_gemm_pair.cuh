@@ -161,11 +161,15 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t sfb_lo0 = smem_u32(smem + S::kOffSfb) >> 4;
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
 
-            auto stage_ready = [&](uint32_t it, uint32_t s, uint32_t ph) {
+            auto stage_wait = [&](uint32_t s, uint32_t ph) {
                 mbar_wait_cluster(&full[s], ph, p.status, 203, s);
                 tcgen05_fence_after();
+            };
+            auto stage_copy_sfa = [&](uint32_t it, uint32_t s) {
+                tcgen05_cp_sf_pair_lohi(sf_tmem0 + (it & 1u) * S::kSfSetCols, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
+            };
+            auto stage_copy_sfb = [&](uint32_t it, uint32_t s) {
                 const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
-                tcgen05_cp_sf_pair_lohi(sf, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
                 tcgen05_cp_sf_pair_lohi(sf + 4, sfb_lo0 + s * (S::kSfbBytes >> 4), hi_sf);
                 tcgen05_cp_sf_pair_lohi(sf + 8, sfb_lo0 + s * (S::kSfbBytes >> 4) + (512u >> 4), hi_sf);
             };
@@ -175,7 +179,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             };
 
             if (total_it > 0) {
-                stage_ready(0, 0, 0);
+                stage_wait(0, 0);
+                stage_copy_sfa(0, 0);
+                stage_copy_sfb(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
             for (uint32_t ti = 0; ti < my_tiles; ++ti) {
@@ -193,12 +199,19 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
                     const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
                     const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
+                    const bool more = it + 1 < total_it;
                     issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    if (more) {
+                        stage_wait(s_next, ph_next);
+                    }
                     issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
-                    if (it + 1 < total_it) {
-                        stage_ready(it + 1, s_next, ph_next);
+                    if (more) {
+                        stage_copy_sfa(it + 1, s_next);
                     }
                     issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    if (more) {
+                        stage_copy_sfb(it + 1, s_next);
+                    }
                     issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
                     tcgen05_commit_pair(&empty[s], 3);
                     s = s_next;
@@ -210,15 +223,16 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         __syncwarp();
     } else if (FUSED_QUANT && warp >= 10) {
         // ------------------------------- quantise-and-push producer -----------------------
-        // Eight of the ten extra warps quantise this rank's shard into the local stage.  The two that
-        // share a scheduler (warp id modulo 4) with the MMA issuer must not compete with that single
-        // thread for issue slots; they run the pusher, a copy loop that issues an instruction only every
-        // few hundred cycles, and send the finished items on to the peers.
-        if ((warp & 3u) != (5u & 3u)) {
+        // Of the fourteen extra warps, eight quantise this rank's shard into the local stage (warps 10-19
+        // except 13 and 17, which share a scheduler with the MMA issuer and must not compete with that
+        // single thread for issue slots).  The other six (13, 17, 20-23) run the pusher, a copy loop that
+        // issues an instruction only every few hundred cycles, and send finished items on to the peers.
+        if (warp < 20u && (warp & 3u) != (5u & 3u)) {
             const uint32_t qw = warp - 10u - (warp > 13u ? 1u : 0u) - (warp > 17u ? 1u : 0u);  // 0..7
-            quant_push_producer(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
+            quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
-            push_worker(p.push, lane, blockIdx.x * 2u + (warp > 13u ? 1u : 0u), gridDim.x * 2u);
+            const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
+            push_worker(p.push, lane, blockIdx.x * kPushWarps + pw, gridDim.x * kPushWarps);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders (both CTAs) ------------------------

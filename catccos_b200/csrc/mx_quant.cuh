@@ -37,6 +37,7 @@ struct QuantPushParams {
     uint32_t rank, world, epoch;
     uint32_t segs_per_chunk;  // a 16-row chunk is split into this many column segments (work items)
     uint32_t seg_cols;        // columns per segment (multiple of 512)
+    uint32_t group_chunks;    // work items are ordered group by group (this many chunks), segment-major inside
     uint32_t num_dst;
     uint8_t* dst_codes[kMaxRanks];   // where this shard's codes [M, K] go at destination d
     uint8_t* dst_scales[kMaxRanks];  // where this shard's scales [M, K/32] go at destination d
@@ -121,6 +122,22 @@ __device__ __forceinline__ void quant_group_sync(uint32_t bar_id)
 
 // Publishing a finished work item: every thread's stores are ordered before the flag words.  The fences
 // are system-scope only when a destination is another GPU; a single-GPU run stays at GPU scope.
+// Order of the work items.  Inside a group of `group_chunks` chunks the items run segment-major (the first
+// K segment of every row of the group first), so a consumer that walks K in order can start early and
+// follow the quantiser; groups follow one another, so a consumer with several waves of tiles gets complete
+// rows for its first wave while the rest is still on its way.  group_chunks >= chunks: one group.
+__device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint32_t segs, uint32_t group_chunks,
+                                           uint32_t& chunk, uint32_t& seg)
+{
+    const uint32_t gc = group_chunks == 0u || group_chunks > chunks ? chunks : group_chunks;
+    const uint32_t per_group = gc * segs;
+    const uint32_t g = item / per_group;
+    const uint32_t rem = item - g * per_group;
+    const uint32_t cg = min(gc, chunks - g * gc);
+    seg = rem / cg;
+    chunk = g * gc + (rem - seg * cg);
+}
+
 // One work item = one (16-row chunk, column segment), owned by exactly one group, which publishes it alone.
 __device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t flag_index, uint32_t tid, uint32_t bar_id)
 {
@@ -145,6 +162,10 @@ __device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t 
 // The producer: a group of 256 threads (tid 0..255) takes work items worker, worker + num_workers, ...
 // and for each quantises (or copies) 16 rows x one column segment, stores the result at every
 // destination and publishes the item's flag.  It never waits on anybody.
+// kPrefetch: the loads of the next 512-column step are issued before the current one is encoded (eight
+// 16-byte loads in flight per lane).  Worth its registers where only one producer group runs per SM
+// (inside the GEMM kernel); the stand-alone kernel prefers more resident CTAs.
+template <bool kPrefetch>
 __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, uint32_t tid, uint32_t worker,
                                                     uint32_t num_workers, uint32_t bar_id)
 {
@@ -158,37 +179,48 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
     const bool device_tiny = p.mode == kQuantDeviceTiny;
 
     for (uint32_t item = worker; item < items; item += num_workers) {
-        // segment-major: the first K segment of every row is published first, so a consumer that walks
-        // K in order can start early and follow the quantiser
-        const uint32_t seg = item / chunks;
-        const uint32_t chunk = item - seg * chunks;
+        uint32_t chunk, seg;
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, chunk, seg);
         const uint32_t c_begin = seg * p.seg_cols;
         const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
         const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
 
-        for (uint32_t cb = c_begin; cb < c_end; cb += kQuantColsPerWarpStep) {
+        auto load_step = [&](uint32_t cb, uint4 (&dst)[2][2]) {
             const uint32_t col = cb + lane * 16;
-            const bool col_ok = col < c_end;
-            uint4 v[2][2];
-            uint4 o[2];
-            uint32_t byte[2];
-            // loads for both rows first (four 16-byte loads in flight per lane)
 #pragma unroll
             for (uint32_t r = 0; r < 2; ++r) {
                 const uint32_t row = row0 + r;
-                v[r][0] = v[r][1] = make_uint4(0, 0, 0, 0);
-                if (col_ok && row < p.M) {
+                dst[r][0] = dst[r][1] = make_uint4(0, 0, 0, 0);
+                if (col < c_end && row < p.M) {
                     if (prequant) {
-                        v[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
-                                                                       (size_t)row * p.K + col));
+                        dst[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
+                                                                         (size_t)row * p.K + col));
                     } else {
                         const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.in) +
                                                                           (size_t)row * p.K + col);
-                        v[r][0] = __ldcs(src);
-                        v[r][1] = __ldcs(src + 1);
+                        dst[r][0] = __ldcs(src);
+                        dst[r][1] = __ldcs(src + 1);
                     }
                 }
             }
+        };
+        uint4 v[2][2], vn[2][2];
+        if (kPrefetch) {
+            load_step(c_begin, v);
+        }
+        for (uint32_t cb = c_begin; cb < c_end; cb += kQuantColsPerWarpStep) {
+            const uint32_t col = cb + lane * 16;
+            const bool col_ok = col < c_end;
+            const bool has_next = kPrefetch && cb + kQuantColsPerWarpStep < c_end;
+            if (kPrefetch) {
+                if (has_next) {
+                    load_step(cb + kQuantColsPerWarpStep, vn);
+                }
+            } else {
+                load_step(cb, v);  // both rows first: four 16-byte loads in flight per lane
+            }
+            uint4 o[2];
+            uint32_t byte[2];
 #pragma unroll
             for (uint32_t r = 0; r < 2; ++r) {
                 const uint32_t row = row0 + r;
@@ -226,6 +258,13 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
                     }
                 }
             }
+            if (has_next) {
+#pragma unroll
+                for (uint32_t r = 0; r < 2; ++r) {
+                    v[r][0] = vn[r][0];
+                    v[r][1] = vn[r][1];
+                }
+            }
         }
         if (p.publish) {
             publish_item(p, chunk * p.segs_per_chunk + seg, tid, bar_id);
@@ -242,7 +281,7 @@ struct PushParams {
     uint8_t* dst_scales[kMaxRanks];
     uint32_t* dst_flags[kMaxRanks];  // rank d's flag words for this source
     uint32_t M, K, rank, world, epoch;
-    uint32_t segs_per_chunk, seg_cols;
+    uint32_t segs_per_chunk, seg_cols, group_chunks;
     uint64_t timeout_ns;
     StatusBlock* status;
 };
@@ -267,8 +306,8 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
     for (uint32_t u = worker; u < units; u += num_workers) {
         const uint32_t item = u / peers;
         const uint32_t d = (p.rank + 1 + (u - item * peers)) % p.world;
-        const uint32_t seg = item / chunks;
-        const uint32_t chunk = item - seg * chunks;
+        uint32_t chunk, seg;
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, chunk, seg);
         const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
         if (lane == 0 && !wait_flag_ge(p.src_flags + flag_index, p.epoch, p.timeout_ns)) {
             report_status(p.status, kStatusFlagTimeout, p.rank, chunk, p.epoch);
@@ -278,14 +317,14 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
         const uint32_t cols = min(p.K, c_begin + p.seg_cols) - c_begin;
         const uint32_t r_begin = chunk * kQuantRowsPerItem;
         const uint32_t rows = min(p.M, r_begin + kQuantRowsPerItem) - r_begin;
-        // codes: rows x cols bytes, 16 bytes per lane per step, four steps in flight
+        // codes: rows x cols bytes, 16 bytes per lane per step, eight steps in flight
         const uint32_t per_row = cols / 16;
         const uint32_t n16 = rows * per_row;
-        for (uint32_t i = lane; i < n16; i += 128) {
-            uint4 v[4];
-            size_t off[4];
+        for (uint32_t i = lane; i < n16; i += 256) {
+            uint4 v[8];
+            size_t off[8];
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
+            for (uint32_t j = 0; j < 8; ++j) {
                 const uint32_t e = i + j * 32;
                 const uint32_t r = e / per_row;
                 off[j] = (size_t)(r_begin + r) * p.K + c_begin + (size_t)(e - r * per_row) * 16;
@@ -294,7 +333,7 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
                 }
             }
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
+            for (uint32_t j = 0; j < 8; ++j) {
                 if (i + j * 32 < n16) {
                     *reinterpret_cast<uint4*>(p.dst_codes[d] + off[j]) = v[j];
                 }
@@ -326,7 +365,7 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
 
 __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
 {
-    quant_push_producer(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
+    quant_push_producer<false>(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
 
     if (!p.consume) {
         return;

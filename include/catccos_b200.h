@@ -142,6 +142,8 @@ int catccos_b200_last_status(uint32_t out[4]);
  *                     the single-GPU harness runs all ranks' producers before any consumer.
  *   "cta_pair"        0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2),
  *                     2 = never
+ *   "group_rows"      0 = automatic; else the rows (multiple of 16) the producer finishes and sends as one group
+ *                     when the GEMM runs in several waves (default 256)
  *   "push_mode"       fused kernel only: 0 = the quantise warps fill the local stage and two pusher warps per
  *                     CTA copy finished items to the peers, 1 = the quantise warps store to every rank themselves
  *   "fuse_mode"       0 = the quantise-and-push warps run inside the GEMM kernel (one launch, default),
