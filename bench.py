@@ -322,6 +322,25 @@ def run_gpu(args) -> None:
             else:
                 capi.mx_gemm(codes, scales, b_codes, b_scales, out=c_dev)
 
+        # decode shape (C5): per-call latency over 1000 calls, no L2 flush (weights stay hot, as in a decode loop)
+        dcfg = workloads.CONFIGS["c5_decode"]
+        d_a = torch.from_numpy(workloads.activation_bits(dcfg, rank, seed=0).view(np.int16).copy()).to(dev).view(torch.bfloat16)
+        d_wt = torch.from_numpy(np.ascontiguousarray(workloads.weight_bits(dcfg, rank, seed=0).T).view(np.int16).copy()).to(dev).view(torch.bfloat16)
+        d_wc, d_ws = capi.mx_quant(d_wt)
+        d_b = d_wc.t().contiguous()
+        d_bs = d_ws.t().contiguous().view(dcfg.k // 64, 2, dcfg.n_local).permute(0, 2, 1).contiguous()
+        del d_wt, d_wc, d_ws
+        d_c = torch.empty((world * dcfg.m_local, dcfg.n_local), dtype=torch.bfloat16, device=dev)
+        d_symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(dcfg.m_local, dcfg.k, dcfg.n_local, world), False))
+        d_ms = timed(lambda: capi.mx_quant_allgather_matmul(d_a, d_b, d_bs, d_c, d_symm, world), 1000, 20, flush_l2=False)
+        d_us = np.sort(d_ms) * 1e3
+        d_flops = workloads.gemm_flops(dcfg, world)
+        extras["decode_c5"] = {
+            "workload": f"c5 per rank A bf16 [16,7168], B MXFP8 [7168,4096], C bf16 [{world * 16},4096], 1000 calls",
+            "p50_us": float(d_us[500]), "p99_us": float(d_us[990]),
+            "tflops_per_gpu_at_p50": d_flops / float(d_us[500]) / 1e6,
+            "weight_stream_floor_us": (dcfg.k * dcfg.n_local * 33 / 32) / read_peaks()["hbm_gbs"] / 1e3,
+        }
         u_ms = timed(unfused, 10, 3)
         extras["unfused_baseline"] = {
             "what": "quantise kernel, ncclAllGather of codes and of scales, GEMM kernel on local memory",
