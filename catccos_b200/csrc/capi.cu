@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -100,10 +101,17 @@ constexpr uint32_t kMaxFlags = 24576;           // flag words per source rank: (
 constexpr size_t kFlagsOff = 256u << 10;        // uint32 [kMaxRanks][kMaxFlags]; the first 256 KiB are reserved
 static_assert(kFlagsOff + (size_t)kMaxRanks * kMaxFlags * 4 <= kHeaderBytes, "header layout");
 
+constexpr size_t kSplitKTileBytes = 128u * 256u * 4u;  // one fp32 partial tile of the widest GEMM tile
+
 struct RankCtx {
     int device = 0;
     int num_sms = 0;
     StatusBlock* status = nullptr;  // device memory
+    // split-K scratch of this rank's GEMM launches: one fp32 partial tile and four flag words per SM, and the
+    // count of split launches so far (the flags are epochs).  Launches of one rank are stream-ordered.
+    float* splitk_ws = nullptr;
+    uint32_t* splitk_flags = nullptr;
+    uint32_t splitk_epoch = 0;
     cudaStream_t side = nullptr;    // the producer kernel runs here, beside the GEMM on the caller's stream
     cudaEvent_t fork = nullptr, join = nullptr;
 };
@@ -142,7 +150,9 @@ struct State {
     int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
     int group_rows = 0;      // 0 = automatic; else rows per send group (multiple of 16)
     int push_mode = 0;       // fused kernel: 0 = pusher warps forward the local stage, 1 = quantise warps store to all ranks
-    int fuse_mode = 0;       // 0 = quantise warps inside the GEMM kernel, 1 = two kernels on two streams
+    int fuse_mode = -1;      // -1 = automatic, 0 = quantise warps inside the GEMM kernel, 1 / 2 = two kernels on two
+                             // streams, 3 = (one rank only) quantise kernel, then GEMM kernel, on the caller's stream
+    int split_k = 0;         // 0 = automatic, 1 = never split K, 2..8 = split K in that many parts when it fits
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
 };
@@ -158,6 +168,10 @@ int setup_rank_ctx(RankCtx& rc, int device)
     CUDA_TRY(cudaDeviceGetAttribute(&rc.num_sms, cudaDevAttrMultiProcessorCount, device));
     CUDA_TRY(cudaMalloc(&rc.status, sizeof(StatusBlock)));
     CUDA_TRY(cudaMemset(rc.status, 0, sizeof(StatusBlock)));
+    CUDA_TRY(cudaMalloc(&rc.splitk_ws, (size_t)rc.num_sms * kSplitKTileBytes));
+    CUDA_TRY(cudaMalloc(&rc.splitk_flags, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
+    CUDA_TRY(cudaMemset(rc.splitk_flags, 0, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
+    rc.splitk_epoch = 0;
     int lo = 0, hi = 0;
     CUDA_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     CUDA_TRY(cudaStreamCreateWithPriority(&rc.side, cudaStreamNonBlocking, hi));
@@ -170,6 +184,8 @@ void destroy_rank_ctx(RankCtx& rc)
 {
     cudaSetDevice(rc.device);
     if (rc.status) cudaFree(rc.status);
+    if (rc.splitk_ws) cudaFree(rc.splitk_ws);
+    if (rc.splitk_flags) cudaFree(rc.splitk_flags);
     if (rc.side) cudaStreamDestroy(rc.side);
     if (rc.fork) cudaEventDestroy(rc.fork);
     if (rc.join) cudaEventDestroy(rc.join);
@@ -309,7 +325,8 @@ int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t o
 }
 
 template <uint32_t BLOCK_N, bool B_MN, typename OutT, bool FUSED>
-int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p)
+int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                     bool overlap_predecessor)
 {
     auto kern = mx_gemm_kernel<BLOCK_N, B_MN, OutT, FUSED>;
     static bool attr_done[kMaxRanks * 2] = {};
@@ -320,7 +337,17 @@ int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUt
                                       (int)GemmSmem<BLOCK_N>::kDynamicBytes));
         attr_done[dev] = true;
     }
-    kern<<<grid, FUSED ? kGemmFusedThreads : kGemmThreads, GemmSmem<BLOCK_N>::kDynamicBytes, st>>>(ta, tb, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(FUSED ? kGemmFusedThreads : kGemmThreads);
+    cfg.dynamicSmemBytes = GemmSmem<BLOCK_N>::kDynamicBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap_predecessor ? 1 : 0;
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -371,7 +398,60 @@ int launch_gemm_pair_inst(int max_pairs_hint, uint32_t tiles, cudaStream_t st, c
 // Rough K-tile periods (microseconds) measured on B200 for the three tilings; used only to pick one.
 constexpr double kPeriodPair256 = 0.53, kPeriodSingle256 = 0.53, kPeriodSingle128 = 0.40;
 
-int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p, bool fused_quant = false)
+struct GemmPlan {
+    bool use_pair;
+    uint32_t block_n, ksplit;
+};
+
+// Tiling of one GEMM launch: CTA pairs or single CTAs, tile width, and the number of K parts.
+GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
+{
+    const bool b_mn = g.b_layout == 0;
+    // waves x K-tile period of each candidate (same K for all, so K drops out)
+    const uint32_t m128 = (Mg + 127) / 128, m256 = (Mg + 255) / 256;
+    const uint32_t n128 = (N + 127) / 128, n256 = (N + 255) / 256;
+    const uint32_t sms = (uint32_t)rc.num_sms, max_pairs = sms / 2;
+    auto waves = [](uint32_t tiles, uint32_t slots) { return (double)((tiles + slots - 1) / slots); };
+    const double t_pair = waves(m256 * n256, max_pairs) * kPeriodPair256;
+    const double t_256 = waves(m128 * n256, sms) * kPeriodSingle256;
+    const double t_128 = waves(m128 * n128, sms) * kPeriodSingle128;
+    GemmPlan plan;
+    plan.use_pair = b_mn && (g.cta_pair == 1 || (g.cta_pair == 0 && g.block_n == 0 && t_pair < t_256 && t_pair < t_128));
+    plan.ksplit = 1;
+    uint32_t bn = (uint32_t)g.block_n;
+    // Split K when the tiles would leave at least half of the SMs idle: every (tile, K part) pair gets its
+    // own CTA, the parts' partial tiles meet in this rank's scratch.  Needs the scratch (the allocation-free
+    // entry point has none), an even split and at least four K tiles per part.
+    if (rc.splitk_ws != nullptr && g.split_k != 1 && g.cta_pair != 1) {
+        const uint32_t sbn = (bn == 128 || N <= 128) ? 128u : 256u;
+        const uint32_t stiles = m128 * (sbn == 128 ? n128 : n256);
+        const uint32_t k_tiles = K / kGemmBlockK;
+        // a power of two, at most one part per 32 output columns of the tile
+        const uint32_t cap_opt = g.split_k >= 2 ? (uint32_t)g.split_k : 8u;
+        const uint32_t cap = std::min(std::min(sms / stiles, sbn / 32u), cap_opt);
+        uint32_t s = 1;
+        for (uint32_t t = 2; t <= cap; t *= 2) {
+            if (k_tiles % t == 0 && k_tiles / t >= 4) {
+                s = t;
+            }
+        }
+        if (s >= 2) {
+            plan.ksplit = s;
+            bn = sbn;
+            plan.use_pair = false;
+        }
+    }
+    if (bn != 128 && bn != 256) {
+        bn = (N > 128 && t_256 <= t_128) ? 256 : 128;
+    }
+    plan.block_n = bn;
+    return plan;
+}
+
+// overlap_predecessor: the kernel launched just before on `st` is this library's quantise kernel, whose output
+// the GEMM reads only behind grid_dep_wait(); the GEMM may then be scheduled while that kernel drains.
+int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p, bool fused_quant = false,
+                bool overlap_predecessor = false)
 {
     if (!g.drv.Load()) {
         return CATCCOS_B200_ECUDA;
@@ -389,19 +469,11 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     const bool f16 = g.c_dtype == 1;
     p.status = rc.status;
     p.timeout_ns = g.timeout_ns;
-    // tiling choice: waves x K-tile period of each candidate (same K for all, so K drops out)
-    const uint32_t m128 = (p.Mg + 127) / 128, m256 = (p.Mg + 255) / 256;
-    const uint32_t n128 = (p.N + 127) / 128, n256 = (p.N + 255) / 256;
-    const uint32_t sms = (uint32_t)rc.num_sms, max_pairs = sms / 2;
-    auto waves = [](uint32_t tiles, uint32_t slots) { return (double)((tiles + slots - 1) / slots); };
-    const double t_pair = waves(m256 * n256, max_pairs) * kPeriodPair256;
-    const double t_256 = waves(m128 * n256, sms) * kPeriodSingle256;
-    const double t_128 = waves(m128 * n128, sms) * kPeriodSingle128;
-    bool use_pair = b_mn && (g.cta_pair == 1 || (g.cta_pair == 0 && g.block_n == 0 && t_pair < t_256 && t_pair < t_128));
-    uint32_t bn = (uint32_t)g.block_n;
-    if (bn != 128 && bn != 256) {
-        bn = (p.N > 128 && t_256 <= t_128) ? 256 : 128;
-    }
+    const GemmPlan plan = plan_gemm(rc, p.Mg, p.N, p.K);
+    const bool use_pair = plan.use_pair;
+    const uint32_t bn = plan.block_n, ksplit = plan.ksplit;
+    const uint32_t m256 = (p.Mg + 255) / 256, n256 = (p.N + 255) / 256;
+    const uint32_t max_pairs = (uint32_t)rc.num_sms / 2;
     if (use_pair) {
         CUtensorMap pa, pb;
         int rc2 = encode_map_2d(&pa, a, p.K, p.Mg, kGemmBlockK, 128);
@@ -427,14 +499,21 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     if (rcode != 0) return rcode;
     const uint32_t tiles = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + bn - 1) / bn);
     int grid = (int)(tiles < (uint32_t)rc.num_sms ? tiles : (uint32_t)rc.num_sms);
+    p.ksplit = ksplit;
+    if (ksplit > 1) {
+        grid = (int)(tiles * ksplit);  // <= SMs by construction: all units are resident at once
+        p.splitk_ws = rc.splitk_ws;
+        p.splitk_flags = rc.splitk_flags;
+        p.splitk_epoch = ++rc.splitk_epoch;
+    }
 #define CATCCOS_GEMM_CASE(BN, MN)                                                                     \
     if (bn == BN && b_mn == MN) {                                                                     \
         if (fused_quant) {                                                                            \
-            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p)                  \
-                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p);          \
+            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p, false)           \
+                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p, false);   \
         }                                                                                             \
-        return f16 ? launch_gemm_inst<BN, MN, __half, false>(grid, st, ta, tb, p)                     \
-                   : launch_gemm_inst<BN, MN, __nv_bfloat16, false>(grid, st, ta, tb, p);             \
+        return f16 ? launch_gemm_inst<BN, MN, __half, false>(grid, st, ta, tb, p, overlap_predecessor)        \
+                   : launch_gemm_inst<BN, MN, __nv_bfloat16, false>(grid, st, ta, tb, p, overlap_predecessor); \
     }
     CATCCOS_GEMM_CASE(256, true)
     CATCCOS_GEMM_CASE(256, false)
@@ -519,6 +598,30 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         const uint32_t tiles = ((W * M + 127) / 128) * ((N + 255) / 256);
         q.group_chunks = tiles > (uint32_t)rc.num_sms ? (g.group_rows > 0 ? (uint32_t)g.group_rows / kRowsPerChunk : 16u) : 0u;
     }
+    {
+        // a split-K GEMM on this rank wants the first K segment of each of its K parts first, then the second
+        // of each, ... (every rank takes the same decision)
+        const GemmPlan plan = plan_gemm(rc, W * M, N, K);
+        const uint32_t segs = seg.segs_per_chunk;
+        if (plan.ksplit > 1 && segs <= 32 && segs > 1) {
+            const uint32_t kper = K / kGemmBlockK / plan.ksplit, seg_ktiles = seg.seg_cols / kGemmBlockK;
+            uint32_t start[9];
+            for (uint32_t a = 0; a < plan.ksplit; ++a) {
+                start[a] = a * kper / seg_ktiles;
+            }
+            start[plan.ksplit] = segs;
+            uint32_t n = 0;
+            for (uint32_t round = 0; n < segs && round < segs; ++round) {
+                for (uint32_t a = 0; a < plan.ksplit; ++a) {
+                    const uint32_t sg = start[a] + round;
+                    if (sg < start[a + 1]) {
+                        q.seg_order[n++] = (uint8_t)sg;
+                    }
+                }
+            }
+            q.seg_order_n = n == segs ? n : 0u;
+        }
+    }
     for (uint32_t d = 0; d < W; ++d) {
         uint8_t* base = sa->base[d] + stage_off;
         q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
@@ -548,7 +651,17 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     }
     const uint8_t* a_stage = sa->base[rank] + stage_off + L.codes_off;
 
-    if (produce && consume && g.fuse_mode == 0) {
+    // With one rank there is no transfer to hide: the quantise kernel uses every SM for a few microseconds and
+    // the GEMM follows it on the same stream, which measures faster than sharing the SMs between the two.
+    const int fuse_mode = (g.fuse_mode == 3 && W > 1) ? 0 : (g.fuse_mode >= 0 ? g.fuse_mode : (W == 1 ? 3 : 0));
+    if (produce && consume && fuse_mode == 3) {
+        q.publish = 0;
+        rcode = launch_quant_push(rc, st, q, prequant, true);
+        if (rcode != 0) return rcode;
+        p.flags = nullptr;  // stream order is the only dependency
+        return launch_gemm(rc, st, a_stage, b, p, false, true);
+    }
+    if (produce && consume && fuse_mode == 0) {
         // one launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
         // warps of all ranks consume behind them
         p.q = q;
@@ -581,11 +694,13 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         ps.segs_per_chunk = seg.segs_per_chunk;
         ps.seg_cols = seg.seg_cols;
         ps.group_chunks = q.group_chunks;
+        ps.seg_order_n = q.seg_order_n;
+        memcpy(ps.seg_order, q.seg_order, sizeof(ps.seg_order));
         ps.timeout_ns = g.timeout_ns;
         ps.status = rc.status;
         return launch_gemm(rc, st, a_stage, b, p, true);
     }
-    if (produce && consume && g.fuse_mode == 2) {
+    if (produce && consume && fuse_mode == 2) {
         // two launches, GEMM first: its CTAs take the SMs (one each, with the large shared-memory carve-out)
         // and wait on flags; the producer's CTAs need no shared memory and are scheduled beside them
         CUDA_TRY(cudaEventRecord(rc.fork, st));
@@ -1087,8 +1202,10 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.group_rows = (int)value;
     } else if (k == "push_mode" && (value == 0 || value == 1)) {
         g.push_mode = (int)value;
-    } else if (k == "fuse_mode" && value >= 0 && value <= 2) {
+    } else if (k == "fuse_mode" && value >= -1 && value <= 3) {
         g.fuse_mode = (int)value;
+    } else if (k == "split_k" && value >= 0 && value <= 8) {
+        g.split_k = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
         g.quant_items_per_sm = (int)value;
     } else {

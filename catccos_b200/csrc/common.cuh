@@ -72,6 +72,39 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p)
     return v;
 }
 
+// The same pair at GPU scope, for flags that never leave this GPU.
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t want, uint64_t timeout_ns)
+{
+    if ((int32_t)(ld_acquire_gpu(flag) - want) >= 0) {
+        return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if ((int32_t)(ld_acquire_gpu(flag) - want) >= 0) {
+            return true;
+        }
+        if ((++spins & 0x3Fu) == 0u) {
+            if (globaltimer_ns() - t0 > timeout_ns) {
+                return false;
+            }
+            __nanosleep(32);
+        }
+    }
+}
+
 // Waits until *flag >= want (epochs only grow).  Returns false when timeout_ns ran out.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t timeout_ns)
 {
@@ -187,6 +220,36 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+
+__device__ __forceinline__ float4 ld_shared_v4(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+// Untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream still runs; grid_dep_wait() then blocks until the predecessor has
+// finished and its writes are visible (and returns at once in a plain launch).  grid_dep_launch() in the
+// predecessor lets the successor's CTAs be scheduled as soon as SM resources allow.
+__device__ __forceinline__ void grid_dep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dep_launch()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap)

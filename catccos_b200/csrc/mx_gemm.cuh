@@ -64,6 +64,14 @@ struct GemmParams {
     StatusBlock* status;
     QuantPushParams q;  // the producer's work when the quantise warps ride in this kernel (local stage only)
     PushParams push;    // the pusher warps' work: local stage -> the peers' stages
+    // Split K (ksplit > 1): K is cut in ksplit equal parts and every (tile, part) pair is a work unit of its
+    // own CTA (units == grid, so all of them are resident together).  Every part owns an equal share of the
+    // tile's columns, writes the rest of its fp32 partial tile to the workspace, and adds the other parts'
+    // pieces of its own columns in ascending part order.  ksplit is a power of two <= BLOCK_N / 32.
+    uint32_t ksplit;
+    float* splitk_ws;        // [tiles][ksplit][BLOCK_N / 32][128][32]
+    uint32_t* splitk_flags;  // [tiles][ksplit][4] epoch words, one per epilogue warp
+    uint32_t splitk_epoch;
 };
 
 template <uint32_t BLOCK_N>
@@ -81,7 +89,7 @@ struct GemmSmem {
     static constexpr uint32_t kOffBar = kOffSfb + kStages * kSfbBytes;
     // barriers: full[S] (TMA bytes + one scale-loader arrival), empty[S], tmem_full[2], tmem_empty[2],
     // overlap_free[2]
-    static constexpr uint32_t kNumBars = 2 * kStages + 6;
+    static constexpr uint32_t kNumBars = 2 * kStages + 6 + 4;  // + one per epilogue warp for the split-K reduction
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack to align the base to 1024 bytes
@@ -167,6 +175,33 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b)
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Writes 32 consecutive columns of one output row from fp32 accumulator values.
+template <typename OutT>
+__device__ __forceinline__ void store_c_chunk(OutT* c, const GemmParams& p, uint32_t row, uint32_t col, const uint32_t (&r)[32])
+{
+    if (row < p.Mg && col < p.N) {
+        OutT* dst = c + (size_t)row * p.N + col;
+        if (col + 32u <= p.N) {
+#pragma unroll
+            for (uint32_t v = 0; v < 2; ++v) {
+                uint32_t o[8];
+#pragma unroll
+                for (uint32_t e = 0; e < 8; ++e) {
+                    o[e] = pack2<OutT>(__uint_as_float(r[v * 16 + 2 * e]), __uint_as_float(r[v * 16 + 2 * e + 1]));
+                }
+                st_global_v8(dst + v * 16, o);  // one full 32-byte sector per store
+            }
+        } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 32u; ++j) {
+                if (col + j < p.N) {
+                    dst[j] = static_cast<OutT>(__uint_as_float(r[j]));
+                }
+            }
+        }
+    }
+}
+
 template <uint32_t BLOCK_N, bool B_MN_MAJOR, typename OutT, bool FUSED_QUANT>
 __global__ void __launch_bounds__(FUSED_QUANT ? kGemmFusedThreads : kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
@@ -183,6 +218,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* tmem_full = bars + 2 * kStages;
     uint64_t* tmem_empty = tmem_full + 2;
     uint64_t* overlap_free = tmem_empty + 2;
+    uint64_t* red_bar = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -203,6 +239,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(&tmem_empty[a], 4);
             mbar_init(&overlap_free[a], 4);
         }
+        for (uint32_t w = 0; w < 4; ++w) {
+            mbar_init(&red_bar[w], 1);
+        }
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -218,13 +257,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (warp == 4) {
         // ------------------------------- TMA producer -------------------------------------
+        grid_dep_wait();  // A may be the output of the kernel launched just before (no-op for a plain launch)
+        const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
+        const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
+        const uint32_t num_units = num_tiles * ksplit;
         uint32_t it = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+        for (uint32_t unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+            const uint32_t ks = unit / num_tiles;
+            TileCoord tc = tile_coord(unit - ks * num_tiles, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
-            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
-                if (p.flags != nullptr && kt % p.seg_ktiles == 0) {
+            const uint32_t kt0 = ks * kper;
+            for (uint32_t kt = kt0; kt < kt0 + kper; ++kt, ++it) {
+                if (p.flags != nullptr && (kt == kt0 || kt % p.seg_ktiles == 0)) {
                     wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
                     fence_proxy_async_all();
                 }
@@ -259,8 +304,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // scale-factor sets in tensor memory), and only then queues the last two MMAs.
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR);
-            const uint32_t my_tiles = (num_tiles > blockIdx.x) ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-            const uint32_t total_it = my_tiles * k_tiles;
+            const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
+            const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
+            const uint32_t num_units = num_tiles * ksplit;
+            const uint32_t my_units = (num_units > blockIdx.x) ? (num_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+            const uint32_t total_it = my_units * kper;
 
             // descriptor halves: the high words are constants, the low words are start addresses >> 4
             const uint32_t hi_ab = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
@@ -308,7 +356,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 stage_copy_sfb(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
-            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
+            for (uint32_t ti = 0; ti < my_units; ++ti) {
                 const uint32_t acc = ti & 1u;
                 const uint32_t acc_ph = (ti >> 1) & 1u;
                 const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
@@ -317,7 +365,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     mbar_wait(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 102, acc);
                 }
                 tcgen05_fence_after();
-                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                for (uint32_t kt = 0; kt < kper; ++kt, ++it) {
                     const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
                     const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
                     const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
@@ -366,17 +414,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // scales of a 64-deep K group together), and stores them as 16-byte atom rows.
         constexpr uint32_t kNB = BLOCK_N / 32;  // B words per lane
         const uint32_t j = warp - 6;
+        grid_dep_wait();  // the A scales may be the output of the kernel launched just before
         const uint32_t sf_row_bytes = p.K / 32;
-        const uint32_t my_tiles = (num_tiles > blockIdx.x) ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-        const uint32_t total_it = my_tiles * k_tiles;
+        const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
+        const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
+        const uint32_t num_units = num_tiles * ksplit;
+        const uint32_t my_units = (num_units > blockIdx.x) ? (num_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+        const uint32_t total_it = my_units * kper;
         uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
         uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
         uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
 
         auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
-            const uint32_t seq = it / k_tiles;
-            const uint32_t kt = it - seq * k_tiles;
-            TileCoord tc = tile_coord(blockIdx.x + seq * gridDim.x, n_tiles, m_tiles, p);
+            const uint32_t seq = it / kper;
+            const uint32_t unit = blockIdx.x + seq * gridDim.x;
+            const uint32_t ks = unit / num_tiles;
+            const uint32_t kt = ks * kper + (it - seq * kper);
+            TileCoord tc = tile_coord(unit - ks * num_tiles, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
             if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
@@ -448,8 +502,116 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t q = warp;  // TMEM lane quarter == warp index modulo 4
         OutT* c = reinterpret_cast<OutT*>(p.c);
         constexpr uint32_t kChunks = BLOCK_N / 32;
+        const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
+        const uint32_t num_units = num_tiles * ksplit;
+        if (ksplit > 1u) {
+            // Split K: this CTA is work unit blockIdx.x = (tile, part ks) and the only one on its SM.  Each part
+            // owns kChunks / ksplit of the tile's 32-column chunks.  A part first writes the chunks it does not
+            // own to its partial tile in the workspace ([part][chunk][128 rows x 32 floats], 4 KiB per chunk and
+            // warp) and raises a flag per epilogue warp; then lane 0 of every warp pulls the other parts' pieces
+            // of the owned chunks into the (now idle) operand stages with bulk copies, all in flight at once,
+            // and the warp adds them to its own accumulator in ascending part order and writes C.
+            const uint32_t unit = blockIdx.x;
+            const uint32_t ks = unit / num_tiles;
+            const uint32_t tile = unit - ks * num_tiles;
+            TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
+            const uint32_t m0 = tc.m_tile * kGemmBlockM;
+            const uint32_t n0 = tc.n_tile * BLOCK_N;
+            const uint32_t row = m0 + q * 32 + lane;
+            const uint32_t cps = kChunks / ksplit;
+            const uint32_t own0 = ks * cps;
+            constexpr size_t kPartFloats = (size_t)kGemmBlockM * BLOCK_N;
+            constexpr uint32_t kPieceBytes = 32u * 32u * 4u;  // 32 rows x 32 floats
+            float* parts = p.splitk_ws + (size_t)tile * ksplit * kPartFloats;
+            uint32_t* flags = p.splitk_flags + (size_t)tile * ksplit * 4u;
+            mbar_wait(&tmem_full[0], 0, p.status, 106, 0);
+            tcgen05_fence_after();
+            // a warp whose 32 rows all lie below the matrix has nothing to add up (its peers in the other
+            // parts take the same decision, so nobody waits for its flag); lanes below the matrix skip
+            // their partial stores
+            const bool warp_rows = m0 + q * 32u < p.Mg;
+            const bool lane_row = row < p.Mg;
+            for (uint32_t chunk = 0; warp_rows && chunk < kChunks; ++chunk) {
+                if (chunk - own0 < cps) {
+                    continue;
+                }
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + chunk * 32u, r);
+                tmem_ld_wait();
+                // inside a 4 KiB piece (32 rows x 32 floats) the 16-byte vector v of row `lane` sits at slot
+                // v * 32 + lane: every store instruction of the warp covers 512 contiguous bytes, and the
+                // reader's shared-memory loads are free of bank conflicts
+                float4* dst = reinterpret_cast<float4*>(parts + ks * kPartFloats + ((size_t)chunk * kGemmBlockM + q * 32u) * 32u) + lane;
+#pragma unroll
+                for (uint32_t v = 0; v < 8; ++v) {
+                    if (lane_row) {
+                        dst[v * 32u] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                   __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
+                }
+            }
+            __syncwarp();  // every lane's partial stores are ordered before lane 0's release
+            uint8_t* red = smem + S::kOffA + q * ((kChunks - 1u) * kPieceBytes);
+            if (warp_rows) {
+                if (lane == 0) {
+                    st_release_gpu(flags + ks * 4u + q, p.splitk_epoch);
+                }
+                // lanes 0 .. ksplit-1 each watch one part's flag (the polls overlap instead of queueing up)
+                if (lane < ksplit && lane != ks && !wait_flag_ge_gpu(flags + lane * 4u + q, p.splitk_epoch, p.timeout_ns)) {
+                    report_status(p.status, kStatusFlagTimeout, 0x100u + lane, tile, p.splitk_epoch);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&red_bar[q], (ksplit - 1u) * cps * kPieceBytes);
+                    fence_proxy_async_all();  // the other parts' generic-proxy stores before this thread's bulk copies
+                    uint32_t slot = 0;
+                    for (uint32_t part = 0; part < ksplit; ++part) {
+                        if (part == ks) {
+                            continue;
+                        }
+                        for (uint32_t oc = 0; oc < cps; ++oc, ++slot) {
+                            bulk_load(red + slot * kPieceBytes,
+                                      parts + part * kPartFloats + ((size_t)(own0 + oc) * kGemmBlockM + q * 32u) * 32u,
+                                      kPieceBytes, &red_bar[q]);
+                        }
+                    }
+                }
+                __syncwarp();
+                mbar_wait(&red_bar[q], 0, p.status, 107, q);
+                for (uint32_t oc = 0; oc < cps; ++oc) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (own0 + oc) * 32u, r);
+                    tmem_ld_wait();
+                    for (uint32_t pi = 0; pi + 1u < ksplit; ++pi) {
+                        // four 16-byte loads at a time: enough to hide the shared-memory latency without
+                        // crowding the 32 accumulator registers
+                        const uint32_t src = smem_u32(red + (pi * cps + oc) * kPieceBytes + lane * 16u);
+#pragma unroll
+                        for (uint32_t h = 0; h < 2; ++h) {
+                            float4 f[4];
+#pragma unroll
+                            for (uint32_t v = 0; v < 4; ++v) {
+                                f[v] = ld_shared_v4(src + (h * 4u + v) * 512u);
+                            }
+#pragma unroll
+                            for (uint32_t v = 0; v < 4; ++v) {
+                                const uint32_t e = (h * 4u + v) * 4u;
+                                r[e] = __float_as_uint(__uint_as_float(r[e]) + f[v].x);
+                                r[e + 1] = __float_as_uint(__uint_as_float(r[e + 1]) + f[v].y);
+                                r[e + 2] = __float_as_uint(__uint_as_float(r[e + 2]) + f[v].z);
+                                r[e + 3] = __float_as_uint(__uint_as_float(r[e + 3]) + f[v].w);
+                            }
+                        }
+                    }
+                    store_c_chunk<OutT>(c, p, row, n0 + (own0 + oc) * 32u, r);
+                }
+            }
+            tcgen05_fence_before();
+        }
         uint32_t ti = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
+        for (uint32_t unit = blockIdx.x; ksplit == 1u && unit < num_units; unit += gridDim.x, ++ti) {
+            const uint32_t ks = unit / num_tiles;
+            const uint32_t tile = unit - ks * num_tiles;
             TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
@@ -476,28 +638,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         mbar_arrive(&overlap_free[acc]);
                     }
                 }
-                const uint32_t col = n0 + chunk * 32u;
-                if (row < p.Mg && col < p.N) {
-                    OutT* dst = c + (size_t)row * p.N + col;
-                    if (col + 32u <= p.N) {
-#pragma unroll
-                        for (uint32_t v = 0; v < 2; ++v) {
-                            uint32_t o[8];
-#pragma unroll
-                            for (uint32_t e = 0; e < 8; ++e) {
-                                o[e] = pack2<OutT>(__uint_as_float(r[v * 16 + 2 * e]), __uint_as_float(r[v * 16 + 2 * e + 1]));
-                            }
-                            st_global_v8(dst + v * 16, o);  // one full 32-byte sector per store
-                        }
-                    } else {
-#pragma unroll
-                        for (uint32_t j = 0; j < 32u; ++j) {
-                            if (col + j < p.N) {
-                                dst[j] = static_cast<OutT>(__uint_as_float(r[j]));
-                            }
-                        }
-                    }
-                }
+                store_c_chunk<OutT>(c, p, row, n0 + chunk * 32u, r);
             }
             tcgen05_fence_before();
             __syncwarp();

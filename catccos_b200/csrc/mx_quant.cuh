@@ -38,6 +38,9 @@ struct QuantPushParams {
     uint32_t segs_per_chunk;  // a 16-row chunk is split into this many column segments (work items)
     uint32_t seg_cols;        // columns per segment (multiple of 512)
     uint32_t group_chunks;    // work items are ordered group by group (this many chunks), segment-major inside
+    uint32_t seg_order_n;     // 0, or the number of entries of seg_order
+    uint8_t seg_order[32];    // the order in which the K segments are visited (a split-K consumer wants the first
+                              // segment of each of its K parts first, then the second of each, ...)
     uint32_t num_dst;
     uint8_t* dst_codes[kMaxRanks];   // where this shard's codes [M, K] go at destination d
     uint8_t* dst_scales[kMaxRanks];  // where this shard's scales [M, K/32] go at destination d
@@ -126,8 +129,9 @@ __device__ __forceinline__ void quant_group_sync(uint32_t bar_id)
 // K segment of every row of the group first), so a consumer that walks K in order can start early and
 // follow the quantiser; groups follow one another, so a consumer with several waves of tiles gets complete
 // rows for its first wave while the rest is still on its way.  group_chunks >= chunks: one group.
+// `order` (n entries, n == segs, or n == 0 for the natural order) maps the position in that walk to the segment.
 __device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint32_t segs, uint32_t group_chunks,
-                                           uint32_t& chunk, uint32_t& seg)
+                                           const uint8_t* order, uint32_t order_n, uint32_t& chunk, uint32_t& seg)
 {
     const uint32_t gc = group_chunks == 0u || group_chunks > chunks ? chunks : group_chunks;
     const uint32_t per_group = gc * segs;
@@ -136,6 +140,9 @@ __device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint3
     const uint32_t cg = min(gc, chunks - g * gc);
     seg = rem / cg;
     chunk = g * gc + (rem - seg * cg);
+    if (order_n == segs) {
+        seg = order[seg];
+    }
 }
 
 // One work item = one (16-row chunk, column segment), owned by exactly one group, which publishes it alone.
@@ -180,7 +187,7 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
 
     for (uint32_t item = worker; item < items; item += num_workers) {
         uint32_t chunk, seg;
-        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, chunk, seg);
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
         const uint32_t c_begin = seg * p.seg_cols;
         const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
         const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
@@ -281,7 +288,8 @@ struct PushParams {
     uint8_t* dst_scales[kMaxRanks];
     uint32_t* dst_flags[kMaxRanks];  // rank d's flag words for this source
     uint32_t M, K, rank, world, epoch;
-    uint32_t segs_per_chunk, seg_cols, group_chunks;
+    uint32_t segs_per_chunk, seg_cols, group_chunks, seg_order_n;
+    uint8_t seg_order[32];
     uint64_t timeout_ns;
     StatusBlock* status;
 };
@@ -307,7 +315,7 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
         const uint32_t item = u / peers;
         const uint32_t d = (p.rank + 1 + (u - item * peers)) % p.world;
         uint32_t chunk, seg;
-        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, chunk, seg);
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
         const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
         if (lane == 0 && !wait_flag_ge(p.src_flags + flag_index, p.epoch, p.timeout_ns)) {
             report_status(p.status, kStatusFlagTimeout, p.rank, chunk, p.epoch);
@@ -365,6 +373,7 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
 
 __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
 {
+    grid_dep_launch();  // a GEMM launched behind this kernel may set itself up while the quantiser drains
     quant_push_producer<false>(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
 
     if (!p.consume) {

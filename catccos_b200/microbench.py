@@ -71,6 +71,7 @@ def main():
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--b-layout", type=int, default=0)
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="library option, e.g. split_k=1")
     args = ap.parse_args()
 
     torch.cuda.set_device(0)
@@ -78,6 +79,9 @@ def main():
     capi.set_option("cta_pair", args.cta_pair)
     capi.set_option("block_n", args.block_n)
     capi.set_option("b_layout", args.b_layout)
+    for kv in args.opt:
+        key, value = kv.split("=")
+        capi.set_option(key, int(value))
     m, n, k = args.m, args.n, args.k
     st = torch.cuda.current_stream().cuda_stream
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if args.flush else None

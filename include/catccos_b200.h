@@ -144,10 +144,18 @@ int catccos_b200_last_status(uint32_t out[4]);
  *                     2 = never
  *   "group_rows"      0 = automatic; else the rows (multiple of 16) the producer finishes and sends as one group
  *                     when the GEMM runs in several waves (default 256)
- *   "push_mode"       fused kernel only: 0 = the quantise warps fill the local stage and two pusher warps per
+ *   "push_mode"       fused kernel only: 0 = the quantise warps fill the local stage and six pusher warps per
  *                     CTA copy finished items to the peers, 1 = the quantise warps store to every rank themselves
- *   "fuse_mode"       0 = the quantise-and-push warps run inside the GEMM kernel (one launch, default),
- *                     1 = quantise kernel and GEMM kernel as two launches on two streams
+ *   "fuse_mode"       -1 = automatic (default): 0 with several ranks, 3 with one;
+ *                     0 = the quantise-and-push warps run inside the GEMM kernel (one launch),
+ *                     1 = quantise kernel and GEMM kernel as two launches on two streams, the GEMM gated on flags,
+ *                     2 = the same two launches with the GEMM launched first,
+ *                     3 = one rank only: quantise kernel, then GEMM kernel, on the caller's stream (no flags)
+ *   "split_k"         0 = automatic: when the output tiles would occupy at most half of the SMs, K is cut in up to
+ *                     eight equal parts, each (tile, part) runs on its own SM and the fp32 partial tiles are added
+ *                     in part order through a per-rank scratch allocated when the rank is set up; 1 = never;
+ *                     2..8 = at most that many parts.  Because of that scratch (and the symmetric buffer's
+ *                     epochs) the operator calls of one rank must not overlap on the GPU.
  *   "publish_scope"   0 = automatic, 1 = system-scope fences, 2 = GPU-scope fences (tuning / diagnosis)
  *   "quant_items_per_sm" work items per SM the quantise kernel aims for (default 4) */
 int catccos_b200_set_option(const char* key, int64_t value);

@@ -74,7 +74,7 @@ def main():
                                              b_d, bs_d, c2, symm, world)
                 status_ok((name, "prequant"))
                 assert torch.equal(c2, c), "pre-quantised and fused paths must agree bit for bit"
-        capi.set_option("fuse_mode", 0)
+        capi.set_option("fuse_mode", -1)
         capi.symm_free(symm)
     capi.finalize()
     print(f"rank {rank} OK", flush=True)

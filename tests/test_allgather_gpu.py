@@ -86,7 +86,8 @@ def _agmm_round(capi, torch, call, world):
 
 
 @pytest.mark.parametrize("cta_pair", [2, 1])
-@pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272)])
+@pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272),
+                                         (2, 16, 7168, 512), (4, 48, 4096, 272)])  # the last two: K split in 8 and 4 parts
 def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n, cta_pair):
     torch = cuda
     local_world(world)
@@ -128,11 +129,39 @@ def test_prequantised_allgather_matmul_emulated(capi, cuda, oracle, local_world,
         assert bad == 0, (r, bad, maxdiff)
 
 
+@pytest.mark.parametrize("fuse_mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("m,k,n", [(16, 7168, 1024), (200, 3584, 528)])
+def test_fused_single_rank_split_k(capi, cuda, oracle, fuse_mode, m, k, n):
+    # few output tiles: K is split over the idle SMs and the quantiser feeds the K parts round-robin
+    torch = cuda
+    capi.finalize()
+    capi.set_option("fuse_mode", fuse_mode)
+    cfg = workloads.Config("t", m, k, n, (1,), "normal", "")
+    bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=11))
+    symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(m, k, n, 1), False))
+    b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
+    try:
+        for call in range(3):
+            a_bits = workloads.activation_bits(cfg, 0, seed=20 + call)
+            a_d = to_dev_bf16(torch, a_bits)
+            c_d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+            capi.mx_quant_allgather_matmul(a_d, b_d, bs_d, c_d, symm, 1)
+            code, st = capi.last_status()
+            assert code == 0, st
+            ac, asc = oracle.quantize_rows(a_bits)
+            gold = oracle.allgather_matmul([ac], [asc], bc, bs)
+            bad, maxdiff = oracle.check_close(c_d.float().cpu().numpy(), gold, 1e-2, 1e-3)
+            assert bad == 0, (call, bad, maxdiff)
+    finally:
+        capi.symm_free(symm)
+        capi.set_option("fuse_mode", -1)
+
+
 @pytest.mark.parametrize("cta_pair", [2, 1])
-@pytest.mark.parametrize("fuse_mode", [0, 1])
+@pytest.mark.parametrize("fuse_mode", [0, 1, 3])
 def test_fused_single_rank(capi, cuda, oracle, fuse_mode, cta_pair):
-    # world 1 through the production paths: quantise warps inside the GEMM kernel (0), or the quantise
-    # kernel on a side stream with the GEMM gated on its flags (1)
+    # world 1 through every path: quantise warps inside the GEMM kernel (0), the quantise kernel on a side
+    # stream with the GEMM gated on its flags (1), or one kernel after the other on one stream (3, the default)
     torch = cuda
     capi.finalize()
     capi.set_option("fuse_mode", fuse_mode)
@@ -153,7 +182,7 @@ def test_fused_single_rank(capi, cuda, oracle, fuse_mode, cta_pair):
     bad, maxdiff = oracle.check_close(c_d.float().cpu().numpy(), gold, 1e-2, 1e-3)
     assert bad == 0, (bad, maxdiff)
     capi.symm_free(symm)
-    capi.set_option("fuse_mode", 0)
+    capi.set_option("fuse_mode", -1)
     capi.set_option("cta_pair", 0)
 
 

@@ -142,6 +142,34 @@ def test_linearity_in_scales_at_full_size(capi, cuda, oracle):
     _check(oracle, c1.float().cpu().numpy()[rows], gold, k)
 
 
+# ---- split K (few output tiles: each (tile, K part) on its own SM, partial tiles added in part order) ----
+
+@pytest.mark.parametrize("split_k", [1, 2, 4, 8])
+@pytest.mark.parametrize("block_n", [0, 128])
+def test_split_k_parts(capi, cuda, oracle, split_k, block_n):
+    m, n, k = 200, 528, 4096  # 2 x 3 tiles of 256 columns (one partial in M and in N), 32 K tiles
+    ac, asc, bc, bsc = _rand_problem(oracle, m, n, k, seed=77)
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    capi.set_option("split_k", split_k)
+    try:
+        for _ in range(2):  # the second call meets the first call's partial tiles and flags
+            out = _run(capi, cuda, ac, asc, bc, bsc, block_n=block_n)
+            _check(oracle, out, gold, k)
+        out16 = _run(capi, cuda, ac, asc, bc, bsc, block_n=block_n, f16=True)
+        assert oracle.check_reference_rule(out16, gold, k, bf16=False)[0] == 0
+    finally:
+        capi.set_option("split_k", 0)
+
+
+def test_split_k_uneven_k_falls_back(capi, cuda, oracle):
+    # 7 K tiles: no even split with four or more tiles per part exists, the GEMM runs unsplit
+    m, n, k = 128, 256, 896
+    ac, asc, bc, bsc = _rand_problem(oracle, m, n, k, seed=78)
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    out = _run(capi, cuda, ac, asc, bc, bsc)
+    _check(oracle, out, gold, k)
+
+
 # ---- CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) ----------------------------------------------
 
 def test_pair_single_tile_unit_scales(capi, cuda, oracle):

@@ -5,7 +5,8 @@ handed all of HBM to its own pools at start-up, or a latency-critical loop that 
 device-wide pause of an allocation.  For them the library carries its scratch (the quantised copy of
 A and the ready flags) in a built-in device array.  This test calls that entry point through the C ABI
 twice in a row and checks each result against the regular entry point, which takes its scratch from
-catccos_b200_symm_alloc; both run the same kernels, so the outputs must agree exactly (the file sorts
+catccos_b200_symm_alloc; with K splitting switched off (the allocation-free path has no scratch for partial
+tiles) both run the same kernels, so the outputs must agree exactly (the file sorts
 last so that a run that stops at the first failure has already seen every other test)."""
 import numpy as np
 import pytest
@@ -24,6 +25,7 @@ def test_static_scratch_matches_regular_entry_point_twice(capi, cuda, oracle):
     bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=5))
     b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
     symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(m, k, n, 1), False))
+    capi.set_option("split_k", 1)
     for call in range(2):
         a_bits = workloads.activation_bits(cfg, 0, seed=100 + call)  # new data each call: stale scratch would show
         a_d = to_dev_bf16(torch, a_bits)
@@ -42,6 +44,7 @@ def test_static_scratch_matches_regular_entry_point_twice(capi, cuda, oracle):
         gold = oracle.allgather_matmul([ac], [asc], bc, bs)
         bad, maxdiff = oracle.check_close(got.float().cpu().numpy(), gold, 1e-2, 1e-3)
         assert bad == 0, (call, bad, maxdiff)
+    capi.set_option("split_k", 0)
     capi.symm_free(symm)
 
 
