@@ -54,6 +54,7 @@ def workload_config(world: int) -> dict:
         "b": "E4M3 [K, N_local] + E8M0 [K/64, N_local, 2], from bf16 N(0,0.02)",
         "c": "bf16 [world*m_local, n_local], fp32 accumulate",
         "l2": "flushed between timed steps (256 MiB written, then read back so that no dirty lines remain)",
+        "rank_alignment": "one-word all-reduce on the stream before each timed step's start event (not timed)",
     }
 
 
@@ -238,6 +239,9 @@ def run_gpu(args) -> None:
     def step():
         capi.mx_quant_allgather_matmul(a_dev, b_codes, b_scales, c_dev, symm, world)
 
+    align_word = torch.zeros(1, dtype=torch.float32, device=dev)
+    align_ranks = not args.no_align
+
     def timed(fn, steps, warmup, flush_l2=True):
         for _ in range(warmup):
             fn()
@@ -247,6 +251,10 @@ def run_gpu(args) -> None:
             if flush_l2:
                 flush.fill_(1)  # evict everything ...
                 flush_sink.copy_(flush.view(torch.int32).sum())  # ... and read it back: no dirty lines remain
+            if world > 1 and align_ranks:
+                # a one-word all-reduce on the stream, outside the timed region: the ranks' streams reach the
+                # step within microseconds of each other instead of carrying the flush kernels' jitter into it
+                dist.all_reduce(align_word)
             e0.record()
             fn()
             e1.record()
@@ -416,6 +424,8 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
                     help="library option for catccos_b200_set_option (tuning runs), e.g. --opt push_mode=1")
+    ap.add_argument("--no-align", action="store_true",
+                    help="do not align the ranks' streams with a one-word all-reduce before each timed step")
     ap.add_argument("--lean", action="store_true",
                     help="headline loop only: no quant-allgather / unfused extras, no CPU baseline (profiling runs)")
     args = ap.parse_args()

@@ -404,7 +404,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
-            push_worker(p.push, lane, blockIdx.x * kPushWarps + pw, gridDim.x * kPushWarps);
+            // pusher pw of CTA b is worker pw * grid + b: when there are fewer units than pushers (two ranks) the work
+            // spreads over all SMs instead of filling the first CTAs' six pushers
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------

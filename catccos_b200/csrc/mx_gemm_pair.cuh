@@ -232,7 +232,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
-            push_worker(p.push, lane, blockIdx.x * kPushWarps + pw, gridDim.x * kPushWarps);
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps);  // spread over all SMs
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders (both CTAs) ------------------------

@@ -185,6 +185,29 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
     const bool prequant = p.mode == kQuantPreQuantised;
     const bool device_tiny = p.mode == kQuantDeviceTiny;
 
+    // loads one 512-column step (two rows of this warp) of the item whose first row for this warp is row0
+    auto load_step = [&](uint32_t row0, uint32_t cb, uint32_t c_end, uint4 (&dst)[2][2]) {
+        const uint32_t col = cb + lane * 16;
+#pragma unroll
+        for (uint32_t r = 0; r < 2; ++r) {
+            const uint32_t row = row0 + r;
+            dst[r][0] = dst[r][1] = make_uint4(0, 0, 0, 0);
+            if (col < c_end && row < p.M) {
+                if (prequant) {
+                    dst[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
+                                                                     (size_t)row * p.K + col));
+                } else {
+                    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.in) +
+                                                                      (size_t)row * p.K + col);
+                    dst[r][0] = __ldcs(src);
+                    dst[r][1] = __ldcs(src + 1);
+                }
+            }
+        }
+    };
+    uint4 v[2][2], vn[2][2];
+    bool first_loaded = false;  // kPrefetch: the item's first step was requested while the previous item finished
+
     for (uint32_t item = worker; item < items; item += num_workers) {
         uint32_t chunk, seg;
         item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
@@ -192,28 +215,8 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
         const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
         const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
 
-        auto load_step = [&](uint32_t cb, uint4 (&dst)[2][2]) {
-            const uint32_t col = cb + lane * 16;
-#pragma unroll
-            for (uint32_t r = 0; r < 2; ++r) {
-                const uint32_t row = row0 + r;
-                dst[r][0] = dst[r][1] = make_uint4(0, 0, 0, 0);
-                if (col < c_end && row < p.M) {
-                    if (prequant) {
-                        dst[r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
-                                                                         (size_t)row * p.K + col));
-                    } else {
-                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.in) +
-                                                                          (size_t)row * p.K + col);
-                        dst[r][0] = __ldcs(src);
-                        dst[r][1] = __ldcs(src + 1);
-                    }
-                }
-            }
-        };
-        uint4 v[2][2], vn[2][2];
-        if (kPrefetch) {
-            load_step(c_begin, v);
+        if (kPrefetch && !first_loaded) {
+            load_step(row0, c_begin, c_end, v);
         }
         for (uint32_t cb = c_begin; cb < c_end; cb += kQuantColsPerWarpStep) {
             const uint32_t col = cb + lane * 16;
@@ -221,10 +224,10 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
             const bool has_next = kPrefetch && cb + kQuantColsPerWarpStep < c_end;
             if (kPrefetch) {
                 if (has_next) {
-                    load_step(cb + kQuantColsPerWarpStep, vn);
+                    load_step(row0, cb + kQuantColsPerWarpStep, c_end, vn);
                 }
             } else {
-                load_step(cb, v);  // both rows first: four 16-byte loads in flight per lane
+                load_step(row0, cb, c_end, v);  // both rows first: four 16-byte loads in flight per lane
             }
             uint4 o[2];
             uint32_t byte[2];
@@ -272,6 +275,15 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
                     v[r][1] = vn[r][1];
                 }
             }
+        }
+        first_loaded = false;
+        if (kPrefetch && item + num_workers < items) {
+            // the next item's first step travels while this item is published (a barrier, a fence, the flags)
+            uint32_t chunk2, seg2;
+            item_coord(item + num_workers, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk2, seg2);
+            const uint32_t cb2 = seg2 * p.seg_cols;
+            load_step(chunk2 * kQuantRowsPerItem + warp * 2, cb2, min(p.K, cb2 + p.seg_cols), v);
+            first_loaded = true;
         }
         if (p.publish) {
             publish_item(p, chunk * p.segs_per_chunk + seg, tid, bar_id);
