@@ -152,6 +152,8 @@ struct State {
     int push_mode = 0;       // fused kernel: 0 = pusher warps forward the local stage, 1 = quantise warps store to all ranks
     int fuse_mode = -1;      // -1 = automatic, 0 = quantise warps inside the GEMM kernel, 1 / 2 = two kernels on two
                              // streams, 3 = (one rank only) quantise kernel, then GEMM kernel, on the caller's stream
+    int a_dtype = 0;         // element type of the A codes (what the quantiser writes, what the GEMM reads): 0 = E4M3, 1 = E5M2
+    int b_dtype = 0;         // element type of the B codes the caller passes
     int split_k = 0;         // 0 = automatic, 1 = never split K, 2..8 = split K in that many parts when it fits
     uint64_t timeout_ns = 2000ull * 1000000ull;
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
@@ -289,7 +291,8 @@ void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
     p.segs_per_chunk = (K + seg_cols - 1) / seg_cols;
 }
 
-int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, bool produce)
+int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, bool produce,
+                      bool local_only = false)
 {
     int grid = quant_grid(rc);
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
@@ -304,7 +307,8 @@ int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool pre
     if ((uint32_t)grid > items) grid = (int)items;
     p.produce = produce ? 1u : 0u;
     p.mode = quant_mode(prequant);
-    p.sys_scope = quant_sys_scope(p.world);
+    p.e5m2 = g.a_dtype == 1 ? 1u : 0u;
+    p.sys_scope = local_only ? quant_sys_scope(1) : quant_sys_scope(p.world);  // no peer sees these stores directly
     mx_quant_push_kernel<<<grid, kQuantThreads, 0, st>>>(p);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
@@ -469,6 +473,8 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     const bool f16 = g.c_dtype == 1;
     p.status = rc.status;
     p.timeout_ns = g.timeout_ns;
+    p.a_e5m2 = g.a_dtype == 1 ? 1u : 0u;
+    p.b_e5m2 = g.b_dtype == 1 ? 1u : 0u;
     const GemmPlan plan = plan_gemm(rc, p.Mg, p.N, p.K);
     const bool use_pair = plan.use_pair;
     const uint32_t bn = plan.block_n, ksplit = plan.ksplit;
@@ -509,8 +515,8 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
 #define CATCCOS_GEMM_CASE(BN, MN)                                                                     \
     if (bn == BN && b_mn == MN) {                                                                     \
         if (fused_quant) {                                                                            \
-            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p, false)           \
-                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p, false);   \
+            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p, overlap_predecessor)        \
+                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p, overlap_predecessor); \
         }                                                                                             \
         return f16 ? launch_gemm_inst<BN, MN, __half, false>(grid, st, ta, tb, p, overlap_predecessor)        \
                    : launch_gemm_inst<BN, MN, __nv_bfloat16, false>(grid, st, ta, tb, p, overlap_predecessor); \
@@ -661,17 +667,19 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         p.flags = nullptr;  // stream order is the only dependency
         return launch_gemm(rc, st, a_stage, b, p, false, true);
     }
-    if (produce && consume && fuse_mode == 0) {
+    if (produce && consume && (fuse_mode == 0 || fuse_mode == 4)) {
         // one launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
         // warps of all ranks consume behind them
         p.q = q;
         p.q.produce = 1;
         p.q.mode = quant_mode(prequant);
+        p.q.e5m2 = g.a_dtype == 1 ? 1u : 0u;
         if (g.push_mode == 1) {
             p.q.sys_scope = quant_sys_scope(W);
             return launch_gemm(rc, st, a_stage, b, p, true);
         }
         p.q.sys_scope = 0;
+        const bool quant_first = fuse_mode == 4;
         PushParams& ps = p.push;
         ps.src_codes = q.dst_codes[rank];
         ps.src_scales = q.dst_scales[rank];
@@ -698,7 +706,16 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         memcpy(ps.seg_order, q.seg_order, sizeof(ps.seg_order));
         ps.timeout_ns = g.timeout_ns;
         ps.status = rc.status;
-        return launch_gemm(rc, st, a_stage, b, p, true);
+        if (quant_first) {
+            // the quantiser runs first, alone on every SM (48 resident warps per SM instead of the eight inside
+            // the GEMM kernel) and fills the local stage (p.q names no peer any more); the GEMM-and-push kernel
+            // follows on the same stream and may be scheduled while the quantiser drains
+            QuantPushParams ql = p.q;
+            rcode = launch_quant_push(rc, st, ql, prequant, true, true);
+            if (rcode != 0) return rcode;
+            p.q.produce = 0;
+        }
+        return launch_gemm(rc, st, a_stage, b, p, true, quant_first);
     }
     if (produce && consume && fuse_mode == 2) {
         // two launches, GEMM first: its CTAs take the SMs (one each, with the large shared-memory carve-out)
@@ -1202,8 +1219,12 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.group_rows = (int)value;
     } else if (k == "push_mode" && (value == 0 || value == 1)) {
         g.push_mode = (int)value;
-    } else if (k == "fuse_mode" && value >= -1 && value <= 3) {
+    } else if (k == "fuse_mode" && value >= -1 && value <= 4) {
         g.fuse_mode = (int)value;
+    } else if (k == "a_dtype" && (value == 0 || value == 1)) {
+        g.a_dtype = (int)value;
+    } else if (k == "b_dtype" && (value == 0 || value == 1)) {
+        g.b_dtype = (int)value;
     } else if (k == "split_k" && value >= 0 && value <= 8) {
         g.split_k = (int)value;
     } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
@@ -1326,6 +1347,7 @@ extern "C" int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_b
     q.publish = 1;
     q.produce = 1;
     q.mode = quant_mode(false);
+    q.e5m2 = g.a_dtype == 1 ? 1u : 0u;
     q.sys_scope = 0;
     q.segs_per_chunk = seg.segs_per_chunk;
     q.seg_cols = seg.seg_cols;

@@ -54,6 +54,7 @@ struct GemmParams {
     const uint8_t* b_scales;  // [K/64, N, 2]
     void* c;                  // [Mg, N]
     uint32_t Mg, N, K;
+    uint32_t a_e5m2, b_e5m2;  // element type of the A / B codes: 0 = E4M3, 1 = E5M2
     // gating on the quantise-and-push kernel (flags == nullptr: all of A is already in place)
     const uint32_t* flags;  // [world][flag_stride] epoch words in this GPU's symmetric header,
                             // word chunk * segs + seg covers 16 rows x (seg_ktiles * 128) columns of K
@@ -303,7 +304,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // are queued it waits for the next stage and copies its scale atoms (into the other of two
         // scale-factor sets in tensor memory), and only then queues the last two MMAs.
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR);
+            const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR) | (p.a_e5m2 ? (1u << 7) : 0u) |
+                                   (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
             const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
             const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
             const uint32_t num_units = num_tiles * ksplit;

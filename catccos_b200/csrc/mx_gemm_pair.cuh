@@ -147,7 +147,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // Same look-ahead as the single-CTA kernel: the next stage is awaited and its scale atoms copied
         // between the second and third MMA of the current K tile.
         if (cta == 0 && lane == 0) {
-            constexpr uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, true);
+            const uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, true) | (p.a_e5m2 ? (1u << 7) : 0u) |
+                                   (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
             const uint32_t my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
             const uint32_t total_it = my_tiles * k_tiles;
 

@@ -31,6 +31,7 @@ struct QuantPushParams {
     const uint8_t* in_scales; // pre-quantised push only: E8M0 [M, K/32]
     uint32_t M, K;
     uint32_t mode;            // kQuantGolden / kQuantDeviceTiny / kQuantPreQuantised
+    uint32_t e5m2;            // 0 = E4M3 codes (emax 8, +-448), 1 = E5M2 codes (emax 15, +-57344)
     uint32_t produce;         // 0: skip the producer part (the harness that runs the two parts apart)
     uint32_t publish;         // 0: nobody waits on this shard's flags (single rank, plain quantise)
     uint32_t sys_scope;       // 1: some destination is another GPU (system-scope fences), 0: all local
@@ -73,24 +74,35 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi)
     return r;
 }
 
-__device__ __forceinline__ uint32_t encode4(uint32_t a, uint32_t b, float mul)
+__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t encode4(uint32_t a, uint32_t b, float mul, bool e5m2)
 {
     const float a0 = __uint_as_float(a << 16) * mul, a1 = __uint_as_float(a & 0xFFFF0000u) * mul;
     const float b0 = __uint_as_float(b << 16) * mul, b1 = __uint_as_float(b & 0xFFFF0000u) * mul;
+    if (e5m2) {
+        return cvt_e5m2x2(a0, a1) | (cvt_e5m2x2(b0, b1) << 16);
+    }
     return cvt_e4m3x2(a0, a1) | (cvt_e4m3x2(b0, b1) << 16);
 }
 
 // Scale byte and multiplier for a block whose largest |bf16 bits| is amax.
-__device__ __forceinline__ void block_scale(uint32_t amax, bool device_tiny, uint32_t& byte, float& mul, bool& nonfinite)
+__device__ __forceinline__ void block_scale(uint32_t amax, bool device_tiny, uint32_t emax, uint32_t& byte, float& mul,
+                                            bool& nonfinite)
 {
     const uint32_t E = amax >> 7;
     nonfinite = (E == 0xFFu);
     if (device_tiny) {
-        byte = E > 8u ? E - 8u : 0u;
+        byte = E > emax ? E - emax : 0u;
         mul = byte == 0u ? 0.0f : __uint_as_float((254u - byte) << 23);
     } else {
         const bool tiny = amax <= 0x2B8Cu;  // |x| < 1e-12 for every bf16 in the block
-        byte = tiny ? 0x7Fu : E - 8u;
+        byte = tiny ? 0x7Fu : E - emax;
         mul = tiny ? 0.0f : __uint_as_float((254u - byte) << 23);
     }
     if (nonfinite) {
@@ -99,18 +111,18 @@ __device__ __forceinline__ void block_scale(uint32_t amax, bool device_tiny, uin
 }
 
 // Quantises 16 bf16 values held by one lane (two lanes share a 32-block).
-__device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, bool device_tiny, uint32_t& byte)
+__device__ __forceinline__ uint4 quant16(uint4 v0, uint4 v1, bool device_tiny, bool e5m2, uint32_t& byte)
 {
     uint32_t amax = max(absmax_bits8(v0), absmax_bits8(v1));
     amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     float mul;
     bool nonfinite;
-    block_scale(amax, device_tiny, byte, mul, nonfinite);
+    block_scale(amax, device_tiny, e5m2 ? 15u : 8u, byte, mul, nonfinite);
     uint4 o;
-    o.x = encode4(v0.x, v0.y, mul);
-    o.y = encode4(v0.z, v0.w, mul);
-    o.z = encode4(v1.x, v1.y, mul);
-    o.w = encode4(v1.z, v1.w, mul);
+    o.x = encode4(v0.x, v0.y, mul, e5m2);
+    o.y = encode4(v0.z, v0.w, mul, e5m2);
+    o.z = encode4(v1.x, v1.y, mul, e5m2);
+    o.w = encode4(v1.z, v1.w, mul, e5m2);
     if (nonfinite) {
         o = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
     }
@@ -184,6 +196,7 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
     const bool sf_vec = (sf_cols % 4u) == 0u;
     const bool prequant = p.mode == kQuantPreQuantised;
     const bool device_tiny = p.mode == kQuantDeviceTiny;
+    const bool e5m2 = p.e5m2 != 0u;
 
     // loads one 512-column step (two rows of this warp) of the item whose first row for this warp is row0
     auto load_step = [&](uint32_t row0, uint32_t cb, uint32_t c_end, uint4 (&dst)[2][2]) {
@@ -241,7 +254,7 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
                         byte[r] = p.in_scales[(size_t)row * sf_cols + col / 32];
                     }
                 } else {
-                    o[r] = quant16(v[r][0], v[r][1], device_tiny, byte[r]);
+                    o[r] = quant16(v[r][0], v[r][1], device_tiny, e5m2, byte[r]);
                 }
                 // scale bytes of 8 lanes (4 blocks) packed into one word on lanes 0, 8, 16, 24
                 const uint32_t base = lane & ~7u;

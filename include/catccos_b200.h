@@ -135,6 +135,10 @@ int catccos_b200_last_status(uint32_t out[4]);
 /* Options (all ranks must set the same values):
  *   "tiny_block_rule" 0 = CPU golden (amax < 1e-12 -> scale 0x7F), 1 = reference device kernel
  *   "c_dtype"         0 = bf16, 1 = fp16 (the reference's output type, main.cpp:28)
+ *   "a_dtype"         element type of the A codes, written by the quantiser and read by the GEMM: 0 = E4M3
+ *                     (emax 8, +-448), 1 = E5M2 (emax 15, +-57344; MX_QUANT_DTYPE = 1 in the reference,
+ *                     comm_block_mx_quant.hpp:75-76,410)
+ *   "b_dtype"         element type of the B codes the caller passes: 0 = E4M3, 1 = E5M2
  *   "b_layout"        0 = b is [k, n] as in the reference files, 1 = b is the transposed copy [n, k]
  *   "block_n"         0 = automatic, 128 or 256 = GEMM tile width
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
@@ -150,7 +154,9 @@ int catccos_b200_last_status(uint32_t out[4]);
  *                     0 = the quantise-and-push warps run inside the GEMM kernel (one launch),
  *                     1 = quantise kernel and GEMM kernel as two launches on two streams, the GEMM gated on flags,
  *                     2 = the same two launches with the GEMM launched first,
- *                     3 = one rank only: quantise kernel, then GEMM kernel, on the caller's stream (no flags)
+ *                     3 = one rank only: quantise kernel, then GEMM kernel, on the caller's stream (no flags),
+ *                     4 = quantise kernel into the local stage first, then the GEMM kernel whose pusher warps
+ *                         forward the stage to the peers (its quantise warps have nothing to do)
  *   "split_k"         0 = automatic: when the output tiles would occupy at most half of the SMs, K is cut in up to
  *                     eight equal parts, each (tile, part) runs on its own SM and the fp32 partial tiles are added
  *                     in part order through a per-rank scratch allocated when the rank is set up; 1 = never;

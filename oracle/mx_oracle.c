@@ -96,6 +96,57 @@ float mxo_e4m3_to_f32(uint8_t c)
     return (c & 0x80) ? -v : v;
 }
 
+/* fp32 -> E5M2, round to nearest even, finite inputs with |v| <= 57344 (callers clamp); NaN -> 0x7F.
+ * E5M2 is the top byte of IEEE half: torch's float8_e5m2 cast used by the golden's "native" backend
+ * (gen_mx_quant_allgather_data.py:48-52,286-287); device cast as for E4M3 (comm_block_mx_quant.hpp:592-603). */
+uint8_t mxo_e5m2_from_f32(float v)
+{
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    uint8_t sign = (uint8_t)((u >> 24) & 0x80);
+    uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) {
+        return 0x7F;
+    }
+    float av;
+    memcpy(&av, &a, 4);
+    if (av > 57344.0f) {
+        av = 57344.0f;
+        memcpy(&a, &av, 4);
+    }
+    if (av < 6.103515625e-05f) { /* below the smallest normal 2^-14: subnormal grid of 2^-16 */
+        float q = rintf(av * 65536.0f);
+        return (uint8_t)(sign | (uint8_t)q);
+    }
+    int e = (int)(a >> 23) - 127; /* -14 .. 15 */
+    uint32_t man = a & 0x7FFFFFu;
+    uint32_t keep = man >> 21;
+    uint32_t rem = man & 0x1FFFFFu;
+    uint32_t code = ((uint32_t)(e + 15) << 2) | keep;
+    if (rem > 0x100000u || (rem == 0x100000u && (keep & 1u))) {
+        code += 1;
+    }
+    return (uint8_t)(sign | (uint8_t)code);
+}
+
+/* E5M2 code -> fp32 (0x7C/0xFC are infinities, 0x7D..0x7F NaN). */
+float mxo_e5m2_to_f32(uint8_t c)
+{
+    uint32_t mag = c & 0x7F;
+    float v;
+    if (mag > 0x7C) {
+        v = NAN;
+    } else if (mag == 0x7C) {
+        v = INFINITY;
+    } else if ((mag >> 2) == 0) {
+        v = (float)(mag & 3) * 1.52587890625e-05f; /* 2^-16 */
+    } else {
+        int e = (int)(mag >> 2) - 15;
+        v = (1.0f + (float)(mag & 3) * 0.25f) * (e >= -126 ? pow2i(e) : 0.0f);
+    }
+    return (c & 0x80) ? -v : v;
+}
+
 /* E8M0 byte -> fp32 scale 2^(byte-127); 0xFF is NaN.  byte 0 is 2^-127 (a subnormal). */
 float mxo_e8m0_to_f32(uint8_t b)
 {
@@ -112,7 +163,7 @@ float mxo_e8m0_to_f32(uint8_t b)
  * returns 0 = normal block (multiply by *mul), 1 = all codes are signed zeros,
  *         2 = block holds Inf/NaN (scale 0xFF, codes 0x7F; device rule,
  *             comm_block_mx_quant.hpp:496,503,513 - no reference test pins this case). */
-static int mxo_block_scale(const uint16_t* x, size_t stride, int mode, uint8_t* scale, float* mul)
+static int mxo_block_scale_fmt(const uint16_t* x, size_t stride, int mode, int emax, uint8_t* scale, float* mul)
 {
     uint16_t amax = 0;
     for (int i = 0; i < MXO_BLOCK; ++i) {
@@ -133,13 +184,13 @@ static int mxo_block_scale(const uint16_t* x, size_t stride, int mode, uint8_t* 
             *scale = 0x7F;
             return 1;
         }
-        *scale = (uint8_t)(E - 8);
-        *mul = pow2i(127 - (E - 8));
+        *scale = (uint8_t)(E - emax);
+        *mul = pow2i(127 - (E - emax));
         return 0;
     }
-    /* device: shared = max(E,8) - 8; byte = shared; recip scale 0 when shared == 0
-     * (comm_block_mx_quant.hpp:498-517). */
-    int byte = E > 8 ? E - 8 : 0;
+    /* device: shared = max(E,emax) - emax; byte = shared; recip scale 0 when shared == 0
+     * (comm_block_mx_quant.hpp:498-517; emax 8 for E4M3, 15 for E5M2, :409-410). */
+    int byte = E > emax ? E - emax : 0;
     *scale = (uint8_t)byte;
     if (byte == 0) {
         return 1;
@@ -148,7 +199,13 @@ static int mxo_block_scale(const uint16_t* x, size_t stride, int mode, uint8_t* 
     return 0;
 }
 
-static inline uint8_t mxo_encode(uint16_t xb, int kind, float mul)
+static int mxo_block_scale(const uint16_t* x, size_t stride, int mode, uint8_t* scale, float* mul)
+{
+    return mxo_block_scale_fmt(x, stride, mode, 8, scale, mul);
+}
+
+/* fmt 0 = E4M3 (max 448), 1 = E5M2 (max 57344) */
+static inline uint8_t mxo_encode_fmt(uint16_t xb, int kind, float mul, int fmt)
 {
     if (kind == 2) {
         return 0x7F;
@@ -156,14 +213,57 @@ static inline uint8_t mxo_encode(uint16_t xb, int kind, float mul)
     if (kind == 1) {
         return (uint8_t)((xb >> 8) & 0x80);
     }
+    const float lim = fmt == 1 ? 57344.0f : 448.0f;
     float y = bf16_to_f32(xb) * mul;
-    if (y > 448.0f) {
-        y = 448.0f;
+    if (y > lim) {
+        y = lim;
     }
-    if (y < -448.0f) {
-        y = -448.0f;
+    if (y < -lim) {
+        y = -lim;
     }
-    return mxo_e4m3_from_f32(y);
+    return fmt == 1 ? mxo_e5m2_from_f32(y) : mxo_e4m3_from_f32(y);
+}
+
+static inline uint8_t mxo_encode(uint16_t xb, int kind, float mul)
+{
+    return mxo_encode_fmt(xb, kind, mul, 0);
+}
+
+/* The E5M2 form of mxo_quantize_rows (MX_QUANT_DTYPE = 1 in the reference: emax 15,
+ * gen_mx_quant_allgather_data.py:48-52; comm_block_mx_quant.hpp:75-76,410). */
+int mxo_quantize_rows_e5m2(const uint16_t* x, size_t rows, size_t K, uint8_t* codes, uint8_t* scales, int mode)
+{
+    if (K % MXO_BLOCK != 0) {
+        return -1;
+    }
+    size_t nb = K / MXO_BLOCK;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t r = 0; r < (ptrdiff_t)rows; ++r) {
+        for (size_t b = 0; b < nb; ++b) {
+            const uint16_t* xb = x + (size_t)r * K + b * MXO_BLOCK;
+            uint8_t s;
+            float mul = 0.0f;
+            int kind = mxo_block_scale_fmt(xb, 1, mode, 15, &s, &mul);
+            scales[(size_t)r * nb + b] = s;
+            for (int i = 0; i < MXO_BLOCK; ++i) {
+                codes[(size_t)r * K + b * MXO_BLOCK + i] = mxo_encode_fmt(xb[i], kind, mul, 1);
+            }
+        }
+    }
+    return 0;
+}
+
+/* Dequantise row-quantised E5M2 codes: out fp32 [rows, K]. */
+void mxo_dequant_rows_e5m2(const uint8_t* codes, const uint8_t* scales, size_t rows, size_t K, float* out)
+{
+    size_t nb = K / MXO_BLOCK;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t r = 0; r < (ptrdiff_t)rows; ++r) {
+        for (size_t k = 0; k < K; ++k) {
+            out[(size_t)r * K + k] =
+                mxo_e5m2_to_f32(codes[(size_t)r * K + k]) * mxo_e8m0_to_f32(scales[(size_t)r * nb + k / MXO_BLOCK]);
+        }
+    }
 }
 
 /* Quantise along the last axis: x bf16 [rows, K] -> codes [rows, K], scales [rows, K/32]

@@ -60,6 +60,14 @@ def lib() -> ctypes.CDLL:
         L.mxo_e4m3_from_f32.restype = ctypes.c_uint8
         L.mxo_e4m3_to_f32.argtypes = [ctypes.c_uint8]
         L.mxo_e4m3_to_f32.restype = ctypes.c_float
+        L.mxo_quantize_rows_e5m2.argtypes = [vp, sz, sz, vp, vp, ci]
+        L.mxo_quantize_rows_e5m2.restype = ci
+        L.mxo_dequant_rows_e5m2.argtypes = [vp, vp, sz, sz, vp]
+        L.mxo_dequant_rows_e5m2.restype = None
+        L.mxo_e5m2_from_f32.argtypes = [ctypes.c_float]
+        L.mxo_e5m2_from_f32.restype = ctypes.c_uint8
+        L.mxo_e5m2_to_f32.argtypes = [ctypes.c_uint8]
+        L.mxo_e5m2_to_f32.restype = ctypes.c_float
         _lib = L
     return _lib
 
@@ -85,13 +93,17 @@ def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------------------
 # C oracle wrappers
 # --------------------------------------------------------------------------------------
-def quantize_rows(x_bits: np.ndarray, mode: int = MODE_GOLDEN):
-    """bf16 bits [rows, K] -> (codes uint8 [rows, K], scales uint8 [rows, K/32])."""
+FMT_E4M3, FMT_E5M2 = 0, 1
+
+
+def quantize_rows(x_bits: np.ndarray, mode: int = MODE_GOLDEN, fmt: int = FMT_E4M3):
+    """bf16 bits [rows, K] -> (codes uint8 [rows, K], scales uint8 [rows, K/32]); codes E4M3 or E5M2."""
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
     rows, K = x_bits.shape
     codes = np.empty((rows, K), np.uint8)
     scales = np.empty((rows, K // 32), np.uint8)
-    if lib().mxo_quantize_rows(_p(x_bits), rows, K, _p(codes), _p(scales), mode) != 0:
+    fn = lib().mxo_quantize_rows_e5m2 if fmt == FMT_E5M2 else lib().mxo_quantize_rows
+    if fn(_p(x_bits), rows, K, _p(codes), _p(scales), mode) != 0:
         raise ValueError("K must be a multiple of 32")
     return codes, scales
 
@@ -107,12 +119,12 @@ def quantize_weight(b_bits: np.ndarray, mode: int = MODE_GOLDEN):
     return codes, scales
 
 
-def dequant_rows(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
+def dequant_rows(codes: np.ndarray, scales: np.ndarray, fmt: int = FMT_E4M3) -> np.ndarray:
     codes = np.ascontiguousarray(codes, dtype=np.uint8)
     scales = np.ascontiguousarray(scales, dtype=np.uint8)
     rows, K = codes.shape
     out = np.empty((rows, K), np.float32)
-    lib().mxo_dequant_rows(_p(codes), _p(scales), rows, K, _p(out))
+    (lib().mxo_dequant_rows_e5m2 if fmt == FMT_E5M2 else lib().mxo_dequant_rows)(_p(codes), _p(scales), rows, K, _p(out))
     return out
 
 
@@ -136,7 +148,7 @@ def gemm_f32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     return c
 
 
-def allgather_matmul(a_codes_per_rank, a_scales_per_rank, b_codes, b_scales, rows=None) -> np.ndarray:
+def allgather_matmul(a_codes_per_rank, a_scales_per_rank, b_codes, b_scales, rows=None, a_fmt: int = FMT_E4M3) -> np.ndarray:
     """Golden C for one rank: concat over ranks of dequant(A_r), times dequant(B); fp32.
 
     ``rows`` optionally selects rows of the gathered A (sampled parity at benchmark sizes).
@@ -145,7 +157,7 @@ def allgather_matmul(a_codes_per_rank, a_scales_per_rank, b_codes, b_scales, row
     a_scales = np.concatenate(a_scales_per_rank, axis=0)
     if rows is not None:
         a_codes, a_scales = a_codes[rows], a_scales[rows]
-    return gemm_f32(dequant_rows(a_codes, a_scales), dequant_weight(b_codes, b_scales))
+    return gemm_f32(dequant_rows(a_codes, a_scales, a_fmt), dequant_weight(b_codes, b_scales))
 
 
 # --------------------------------------------------------------------------------------

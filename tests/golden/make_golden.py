@@ -36,10 +36,10 @@ def bits_f32(b):
     return (b.astype(np.uint32) << np.uint32(16)).view(np.float32)
 
 
-def ref_quant_rows(bits):
+def ref_quant_rows(bits, fmt="E4M3"):
     """Reference quantiser on bf16 inputs -> (codes u8 [M,K], scale bytes u8 [M,K/32])."""
     x = torch.from_numpy(bits_f32(bits).copy())
-    q, scale, _ = ref._quantize_axis_last_fp8(x, "E4M3")
+    q, scale, _ = ref._quantize_axis_last_fp8(x, fmt)
     codes = q.view(torch.uint8).numpy().copy()
     sb = scale.to(torch.float8_e8m0fnu).view(torch.uint8).numpy().copy()
     return codes, sb[:, : bits.shape[1] // 32]
@@ -125,6 +125,22 @@ def main():
         b_scales=sb.view(torch.uint8).numpy().copy(),
         golden=golden.astype(np.float32),
     )
+
+    # 5. the E5M2 output type (MX_QUANT_DTYPE = 1: emax 15, max 57344) on the inputs of 1-3, and the same
+    #    2-rank AllGather-Matmul with E5M2 activations (weights stay E4M3)
+    e5 = {}
+    for tag, xin in (("normal", x), ("outlier", xo), ("edges", xe)):
+        c5, s5 = ref_quant_rows(xin, "E5M2")
+        e5["x_" + tag], e5["codes_" + tag], e5["scales_" + tag] = xin, c5, s5
+    a5_deq, a5_codes, a5_scales = [], [], []
+    for r in range(world):
+        q, scale, deq = ref._quantize_fp8(torch.from_numpy(bits_f32(a_bits[r]).copy()), "E5M2", 1)
+        a5_codes.append(q.view(torch.uint8).numpy().copy())
+        a5_scales.append(scale.to(torch.float8_e8m0fnu).view(torch.uint8).numpy().copy())
+        a5_deq.append(deq)
+    e5["agmm_a_codes"], e5["agmm_a_scales"] = np.stack(a5_codes), np.stack(a5_scales)
+    e5["agmm_golden"] = torch.matmul(torch.cat(a5_deq, dim=0), b_deq).numpy().astype(np.float32)
+    save("quant_e5m2.npz", **e5)
 
 
 if __name__ == "__main__":

@@ -56,8 +56,8 @@ def main():
         bc, bs = mx_oracle.quantize_weight(workloads.weight_bits(cfg, rank, seed=0))
         b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
         b_deq = mx_oracle.dequant_weight(bc, bs)
-        for rnd in range(3):
-            capi.set_option("fuse_mode", 1 if rnd == 2 else 0)  # the last round runs as two kernels
+        for rnd, fuse_mode in enumerate((-1, 0, 4, 1)):  # the default, then every multi-rank variant by name
+            capi.set_option("fuse_mode", fuse_mode)
             bits = [workloads.activation_bits(cfg, r, seed=rnd) for r in range(world)]
             c = torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda")
             capi.mx_quant_allgather_matmul(dev_bf16(bits[rank]), b_d, bs_d, c, symm, world)

@@ -129,7 +129,7 @@ def test_prequantised_allgather_matmul_emulated(capi, cuda, oracle, local_world,
         assert bad == 0, (r, bad, maxdiff)
 
 
-@pytest.mark.parametrize("fuse_mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("fuse_mode", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("m,k,n", [(16, 7168, 1024), (200, 3584, 528)])
 def test_fused_single_rank_split_k(capi, cuda, oracle, fuse_mode, m, k, n):
     # few output tiles: K is split over the idle SMs and the quantiser feeds the K parts round-robin
@@ -157,8 +157,35 @@ def test_fused_single_rank_split_k(capi, cuda, oracle, fuse_mode, m, k, n):
         capi.set_option("fuse_mode", -1)
 
 
+@pytest.mark.parametrize("fuse_mode", [0, 3])
+def test_fused_single_rank_e5m2(capi, cuda, oracle, fuse_mode):
+    # bf16 in, E5M2 codes quantised on the fly and consumed by the GEMM in the same call
+    torch = cuda
+    capi.finalize()
+    capi.set_option("fuse_mode", fuse_mode)
+    capi.set_option("a_dtype", 1)
+    cfg = workloads.Config("t", 272, 2048, 528, (1,), "normal", "")
+    a_bits = workloads.activation_bits(cfg, 0, seed=3)
+    bc, bs = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=3))
+    symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(cfg.m_local, cfg.k, cfg.n_local, 1), False))
+    try:
+        c_d = torch.zeros((cfg.m_local, cfg.n_local), dtype=torch.bfloat16, device="cuda")
+        capi.mx_quant_allgather_matmul(to_dev_bf16(torch, a_bits), torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda(),
+                                       c_d, symm, 1)
+        code, st = capi.last_status()
+        assert code == 0, st
+        ac, asc = oracle.quantize_rows(a_bits, fmt=oracle.FMT_E5M2)
+        gold = oracle.allgather_matmul([ac], [asc], bc, bs, a_fmt=oracle.FMT_E5M2)
+        bad, maxdiff = oracle.check_close(c_d.float().cpu().numpy(), gold, 1e-2, 1e-3)
+        assert bad == 0, (bad, maxdiff)
+    finally:
+        capi.symm_free(symm)
+        capi.set_option("fuse_mode", -1)
+        capi.set_option("a_dtype", 0)
+
+
 @pytest.mark.parametrize("cta_pair", [2, 1])
-@pytest.mark.parametrize("fuse_mode", [0, 1, 3])
+@pytest.mark.parametrize("fuse_mode", [0, 1, 3, 4])
 def test_fused_single_rank(capi, cuda, oracle, fuse_mode, cta_pair):
     # world 1 through every path: quantise warps inside the GEMM kernel (0), the quantise kernel on a side
     # stream with the GEMM gated on its flags (1), or one kernel after the other on one stream (3, the default)

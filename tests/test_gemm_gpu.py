@@ -170,6 +170,31 @@ def test_split_k_uneven_k_falls_back(capi, cuda, oracle):
     _check(oracle, out, gold, k)
 
 
+# ---- E5M2 activations (option "a_dtype" = 1; weights stay E4M3) ----
+
+@pytest.mark.parametrize("cta_pair", [2, 1])
+def test_e5m2_activations(capi, cuda, oracle, golden, cta_pair):
+    d, g = golden("quant_e5m2"), golden("agmm_small")
+    capi.set_option("a_dtype", 1)
+    try:
+        # the reference-generated 2-rank problem
+        out = _run(capi, cuda, np.concatenate(list(d["agmm_a_codes"])), np.concatenate(list(d["agmm_a_scales"])),
+                   g["b_codes"], g["b_scales"], cta_pair=cta_pair)
+        _check(oracle, out, d["agmm_golden"], 256)
+        # a larger seeded problem against the oracle
+        rng = np.random.default_rng(55)
+        m, n, k = 300, 528, 2048
+        a = rng.standard_normal((m, k), dtype=np.float32)
+        b = rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.02)
+        ac, asc = oracle.quantize_rows(workloads.f32_to_bf16_bits(a), fmt=oracle.FMT_E5M2)
+        bc, bsc = oracle.quantize_weight(workloads.f32_to_bf16_bits(b))
+        gold = oracle.allgather_matmul([ac], [asc], bc, bsc, a_fmt=oracle.FMT_E5M2)
+        out = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=cta_pair)
+        _check(oracle, out, gold, k)
+    finally:
+        capi.set_option("a_dtype", 0)
+
+
 # ---- CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) ----------------------------------------------
 
 def test_pair_single_tile_unit_scales(capi, cuda, oracle):

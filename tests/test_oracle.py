@@ -84,6 +84,38 @@ def test_e4m3_codec_round_trip(oracle):
     assert L.mxo_e4m3_from_f32(1000.0) == 0x7E
 
 
+# ---- E5M2 output type (MX_QUANT_DTYPE = 1 in the reference: emax 15, max 57344) ----
+
+@pytest.mark.parametrize("tag", ["normal", "outlier", "edges"])
+def test_e5m2_quantise_matches_reference_golden(oracle, golden, tag):
+    d = golden("quant_e5m2")
+    codes, scales = oracle.quantize_rows(d["x_" + tag], fmt=oracle.FMT_E5M2)
+    assert np.array_equal(scales, d["scales_" + tag])
+    assert np.array_equal(codes, d["codes_" + tag])
+
+
+def test_e5m2_allgather_matmul_matches_reference_golden(oracle, golden):
+    d, g = golden("quant_e5m2"), golden("agmm_small")
+    for r in range(2):  # the generator's own quantiser call (axis 1) agrees with the row quantiser
+        c, s = oracle.quantize_rows(g["a_bits"][r], fmt=oracle.FMT_E5M2)
+        assert np.array_equal(c, d["agmm_a_codes"][r]) and np.array_equal(s, d["agmm_a_scales"][r])
+    out = oracle.allgather_matmul(list(d["agmm_a_codes"]), list(d["agmm_a_scales"]), g["b_codes"], g["b_scales"],
+                                  a_fmt=oracle.FMT_E5M2)
+    assert np.abs(out - d["agmm_golden"]).max() <= 1e-5 * np.abs(d["agmm_golden"]).max()
+
+
+def test_e5m2_codec_round_trip(oracle):
+    L = oracle.lib()
+    for code in range(256):
+        if code & 0x7F >= 0x7C:  # infinities and NaNs
+            continue
+        assert L.mxo_e5m2_from_f32(L.mxo_e5m2_to_f32(code)) == code
+    assert L.mxo_e5m2_from_f32(1.125) == 0x3C   # halfway between 1.0 (0x3C) and 1.25 (0x3D): even code
+    assert L.mxo_e5m2_from_f32(1.375) == 0x3E   # halfway between 1.25 (0x3D) and 1.5 (0x3E)
+    assert L.mxo_e5m2_from_f32(1e9) == 0x7B     # saturates at 57344, never infinity
+    assert L.mxo_e5m2_from_f32(-1e-9) == 0x80
+
+
 def test_workload_shapes_and_determinism():
     cfg = workloads.CONFIGS["c4_outlier"]
     a = workloads.activation_bits(cfg, 2, seed=0, rows=8)

@@ -120,3 +120,39 @@ def test_full_size_checksum_properties(capi, cuda, oracle):
     want_c, want_s = oracle.quantize_rows(x[rows])
     _assert_bit_exact(codes.cpu().numpy()[rows], want_c, "codes")
     _assert_bit_exact(scales.cpu().numpy()[rows], want_s, "scales")
+
+
+# ---- E5M2 output type (option "a_dtype" = 1) ----
+
+@pytest.mark.parametrize("tag", ["normal", "outlier", "edges"])
+def test_e5m2_fixture_parity(capi, cuda, golden, tag):
+    d = golden("quant_e5m2")
+    capi.set_option("a_dtype", 1)
+    try:
+        codes, scales = _quant_gpu(capi, cuda, d["x_" + tag])
+    finally:
+        capi.set_option("a_dtype", 0)
+    _assert_bit_exact(scales, d["scales_" + tag], "scales")
+    _assert_bit_exact(codes, d["codes_" + tag], "codes")
+
+
+def test_e5m2_all_bf16_values(capi, cuda, oracle):
+    # every finite bf16 bit pattern alone in its block, and three binades below the block maximum
+    vals = np.arange(0x10000, dtype=np.uint32)
+    finite = vals[((vals >> 7) & 0xFF) != 0xFF].astype(np.uint16)
+    rows = []
+    for shift in (0, 3):
+        blk = np.zeros((finite.size, 32), np.uint16)
+        blk[:, 0] = finite
+        e = (finite >> 7) & 0xFF
+        blk[:, 1] = np.minimum(e.astype(np.int32) + shift, 254).astype(np.uint16) << 7
+        rows.append(blk)
+    x = np.concatenate(rows).reshape(-1, 32 * 8)
+    want_c, want_s = oracle.quantize_rows(x, fmt=oracle.FMT_E5M2)
+    capi.set_option("a_dtype", 1)
+    try:
+        got_c, got_s = _quant_gpu(capi, cuda, x)
+    finally:
+        capi.set_option("a_dtype", 0)
+    _assert_bit_exact(got_s, want_s, "scales")
+    _assert_bit_exact(got_c, want_c, "codes")
