@@ -94,13 +94,16 @@ struct GemmSmem {
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack to align the base to 1024 bytes
-    // accumulator placement in tensor memory: two 128 x BLOCK_N fp32 accumulators.  For
-    // BLOCK_N = 256 they overlap by 24 columns (232..255) so that 24 columns stay free for two sets of
-    // scale factors; the epilogue drains the shared columns first and then lets the next tile start.
+    // Tensor memory: two 128 x BLOCK_N fp32 accumulators and one set of scale factors per stage (12 columns:
+    // SFA 4, then SFB 4 per 128 columns of N).  For BLOCK_N = 256 the accumulators overlap by 64 columns
+    // (192..255) to leave room for the four sets; the epilogue drains the two shared 32-column chunks first and
+    // then lets the next tile start.
     static constexpr bool kOverlap = (BLOCK_N == 256);
-    static constexpr uint32_t kAccCol1 = kOverlap ? 232 : 256;
-    static constexpr uint32_t kSfCol = 488;       // two scale-factor sets (even / odd K tile), 12 columns each:
-    static constexpr uint32_t kSfSetCols = 12;    // SFA 4 columns, then SFB 4 per 128 columns of N
+    static constexpr uint32_t kOverlapChunks = 2;
+    static constexpr uint32_t kAccCol1 = kOverlap ? 192 : 256;
+    static constexpr uint32_t kSfCol = kOverlap ? 448 : 384;
+    static constexpr uint32_t kSfSetCols = 12;
+    static_assert(kSfCol + kStages * kSfSetCols <= 512, "scale-factor sets must fit in tensor memory");
 };
 
 struct TileCoord {
@@ -317,12 +320,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t hi_b_mn = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
             const uint32_t lo_ab_lbo = (uint32_t)make_smem_desc(0, 16, 1024, 2);         // LBO field of A / K-major B
             const uint32_t lo_b_mn_lbo = (uint32_t)make_smem_desc(0, 16384, 1024, 2);    // LBO field of MN-major B
-            const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
             const uint32_t a_lo0 = lo_ab_lbo | (smem_u32(smem + S::kOffA) >> 4);
             const uint32_t b_lo0 = (B_MN_MAJOR ? lo_b_mn_lbo : lo_ab_lbo) | (smem_u32(smem + S::kOffB) >> 4);
             const uint32_t b_hi = B_MN_MAJOR ? hi_b_mn : hi_ab;
-            const uint32_t sfa_lo0 = smem_u32(smem + S::kOffSfa) >> 4;
-            const uint32_t sfb_lo0 = smem_u32(smem + S::kOffSfb) >> 4;
             constexpr uint32_t kKbStepA = 32u >> 4;                                  // 32 bytes along K
             constexpr uint32_t kKbStepB = (B_MN_MAJOR ? 4096u : 32u) >> 4;          // 32 K rows of 128 bytes, or 32 bytes
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
@@ -332,17 +332,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             auto stage_wait = [&](uint32_t s, uint32_t ph) {
                 mbar_wait(&full[s], ph, p.status, 103, s);
                 tcgen05_fence_after();
-            };
-            auto stage_copy_sfa = [&](uint32_t it, uint32_t s) {
-                // 32 rows x 16 bytes per atom, no swizzle, 8-row groups 128 bytes apart
-                tcgen05_cp_sf_lohi(sf_tmem0 + (it & 1u) * S::kSfSetCols, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
-            };
-            auto stage_copy_sfb = [&](uint32_t it, uint32_t s) {
-                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
-#pragma unroll
-                for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
-                    tcgen05_cp_sf_lohi(sf + 4 + 4 * h, sfb_lo0 + s * (S::kSfbBytes >> 4) + h * (512u >> 4), hi_sf);
-                }
             };
             // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; K advances 32 bytes in the row.
             // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart, 8-row K groups
@@ -354,8 +343,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
             if (total_it > 0) {
                 stage_wait(0, 0);
-                stage_copy_sfa(0, 0);
-                stage_copy_sfb(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
             for (uint32_t ti = 0; ti < my_units; ++ti) {
@@ -370,24 +357,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (uint32_t kt = 0; kt < kper; ++kt, ++it) {
                     const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
                     const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
-                    const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                    const uint32_t sf = sf_tmem0 + s * S::kSfSetCols;
                     const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
                     const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
                     const bool more = it + 1 < total_it;
                     issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
+                    tcgen05_commit(&empty[s]);
                     if (more) {
                         stage_wait(s_next, ph_next);
                     }
-                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
-                    if (more) {
-                        stage_copy_sfa(it + 1, s_next);
-                    }
-                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
-                    if (more) {
-                        stage_copy_sfb(it + 1, s_next);
-                    }
-                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
-                    tcgen05_commit(&empty[s]);
                     s = s_next;
                     ph = ph_next;
                 }
@@ -489,7 +470,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             fence_proxy_async_shared();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&full[s]);
+                // Copy the atoms into tensor memory from here, not from the MMA issuer: one thread gets a tcgen05
+                // instruction out only every ~70 cycles, and four MMAs, three copies and a commit per K tile kept
+                // the issuer behind the tensor pipe.  Every stage has its own scale set in tensor memory, so the
+                // wait for the stage (above) also covers the set; the commit below stands in for this warp's
+                // arrival on the full barrier: the issuer sees the stage only when its scales are in place.
+                tcgen05_fence_after();
+                const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);  // 32 rows x 16 bytes, no swizzle
+                const uint32_t sf_t = tmem_base + S::kSfCol + s * S::kSfSetCols;
+                tcgen05_cp_sf_lohi(sf_t, smem_u32(sfa) >> 4, hi_sf);
+#pragma unroll
+                for (uint32_t h = 0; h < S::kSfbAtoms; ++h) {
+                    tcgen05_cp_sf_lohi(sf_t + 4 + 4 * h, (smem_u32(sfb) >> 4) + h * (512u >> 4), hi_sf);
+                }
+                tcgen05_commit(&full[s]);
             }
             if (has_next) {
 #pragma unroll
@@ -625,17 +619,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_wait(&tmem_full[acc], acc_ph, p.status, 106, acc);
             tcgen05_fence_after();
             const uint32_t row = m0 + q * 32 + lane;
-            // the chunk that holds the columns shared with the other accumulator goes first
-            const uint32_t first = (S::kOverlap && acc == 0) ? (kChunks - 1) : 0u;
+            // the chunks that hold the columns shared with the other accumulator go first: the last two of
+            // accumulator 0, the first two of accumulator 1
             for (uint32_t ci = 0; ci < kChunks; ++ci) {
                 uint32_t chunk = ci;
                 if (S::kOverlap && acc == 0) {
-                    chunk = (ci == 0) ? first : ci - 1;
+                    chunk = ci < S::kOverlapChunks ? kChunks - S::kOverlapChunks + ci : ci - S::kOverlapChunks;
                 }
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + d_col + chunk * 32u, r);
                 tmem_ld_wait();
-                if (S::kOverlap && ci == 0) {
+                if (S::kOverlap && ci == S::kOverlapChunks - 1) {
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) {
