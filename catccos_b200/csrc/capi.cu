@@ -400,7 +400,7 @@ int launch_gemm_pair_inst(int max_pairs_hint, uint32_t tiles, cudaStream_t st, c
 }
 
 // Rough K-tile periods (microseconds) measured on B200 for the three tilings; used only to pick one.
-constexpr double kPeriodPair256 = 0.53, kPeriodSingle256 = 0.53, kPeriodSingle128 = 0.40;
+constexpr double kPeriodPair256 = 0.43, kPeriodSingle256 = 0.47, kPeriodSingle128 = 0.32;
 
 struct GemmPlan {
     bool use_pair;

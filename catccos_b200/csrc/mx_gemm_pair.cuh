@@ -20,7 +20,7 @@ constexpr uint32_t kPairBlockM = 256;
 constexpr uint32_t kPairBlockN = 256;
 
 struct PairSmem {
-    static constexpr uint32_t kStages = 6;
+    static constexpr uint32_t kStages = 5;
     static constexpr uint32_t kABytes = 128 * kGemmBlockK;  // this CTA's 128 rows
     static constexpr uint32_t kBBytes = 128 * kGemmBlockK;  // this CTA's 128 columns
     static constexpr uint32_t kSfaBytes = 512;
@@ -30,13 +30,17 @@ struct PairSmem {
     static constexpr uint32_t kOffSfa = kOffB + kStages * kBBytes;
     static constexpr uint32_t kOffSfb = kOffSfa + kStages * kSfaBytes;
     static constexpr uint32_t kOffBar = kOffSfb + kStages * kSfbBytes;
-    static constexpr uint32_t kNumBars = 2 * kStages + 6;
+    // full[S], empty[S], tmem_full[2], tmem_empty[2], overlap_free[2], atoms_written[S] (leader only: both
+    // CTAs' scale loaders have put a stage's atoms into shared memory)
+    static constexpr uint32_t kNumBars = 3 * kStages + 6;
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;
-    static constexpr uint32_t kAccCol1 = 232;  // the two accumulators share columns 232..255 (see mx_gemm.cuh)
-    static constexpr uint32_t kSfCol = 488;    // two scale-factor sets of 12 columns (even / odd K tile)
+    static constexpr uint32_t kOverlapChunks = 2;
+    static constexpr uint32_t kAccCol1 = 192;  // the two accumulators share columns 192..255 (see mx_gemm.cuh)
+    static constexpr uint32_t kSfCol = 448;    // one scale-factor set of 12 columns per stage
     static constexpr uint32_t kSfSetCols = 12;
+    static_assert(kSfCol + kStages * kSfSetCols <= 512, "scale-factor sets must fit in tensor memory");
 };
 
 // Tile order for pairs: as tile_coord, with 256-row tiles.
@@ -79,6 +83,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* tmem_full = bars + 2 * kStages;
     uint64_t* tmem_empty = tmem_full + 2;
     uint64_t* overlap_free = tmem_empty + 2;
+    uint64_t* atoms_written = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -94,8 +99,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 4);  // per CTA: the producer's expect_tx arrival and one scale-loader warp
+            mbar_init(&full[s], 3);  // both CTAs' producers (expect_tx) and the commit behind the scale copies
             mbar_init(&empty[s], 1);
+            mbar_init(&atoms_written[s], 2);  // one scale-loader warp in each CTA
         }
         for (uint32_t a = 0; a < 2; ++a) {
             mbar_init(&tmem_full[a], 1);
@@ -154,25 +160,14 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
             const uint32_t hi_a = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
             const uint32_t hi_b = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
-            const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
             const uint32_t a_lo0 = (uint32_t)make_smem_desc(0, 16, 1024, 2) | (smem_u32(smem + S::kOffA) >> 4);
             // each CTA holds 128 columns of B (one 128-byte swizzle row per K): MN-major
             const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
-            const uint32_t sfa_lo0 = smem_u32(smem + S::kOffSfa) >> 4;
-            const uint32_t sfb_lo0 = smem_u32(smem + S::kOffSfb) >> 4;
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
 
             auto stage_wait = [&](uint32_t s, uint32_t ph) {
                 mbar_wait_cluster(&full[s], ph, p.status, 203, s);
                 tcgen05_fence_after();
-            };
-            auto stage_copy_sfa = [&](uint32_t it, uint32_t s) {
-                tcgen05_cp_sf_pair_lohi(sf_tmem0 + (it & 1u) * S::kSfSetCols, sfa_lo0 + s * (S::kSfaBytes >> 4), hi_sf);
-            };
-            auto stage_copy_sfb = [&](uint32_t it, uint32_t s) {
-                const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
-                tcgen05_cp_sf_pair_lohi(sf + 4, sfb_lo0 + s * (S::kSfbBytes >> 4), hi_sf);
-                tcgen05_cp_sf_pair_lohi(sf + 8, sfb_lo0 + s * (S::kSfbBytes >> 4) + (512u >> 4), hi_sf);
             };
             auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
                 umma_mxf8_pair_lohi(d_col, a_lo + kb * (32u >> 4), hi_a, b_lo + kb * (4096u >> 4), hi_b,
@@ -181,8 +176,6 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
             if (total_it > 0) {
                 stage_wait(0, 0);
-                stage_copy_sfa(0, 0);
-                stage_copy_sfb(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
             for (uint32_t ti = 0; ti < my_tiles; ++ti) {
@@ -197,24 +190,18 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
                     const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
-                    const uint32_t sf = sf_tmem0 + (it & 1u) * S::kSfSetCols;
+                    const uint32_t sf = sf_tmem0 + s * S::kSfSetCols;
                     const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1;
                     const uint32_t ph_next = ph ^ (s_next == 0u ? 1u : 0u);
                     const bool more = it + 1 < total_it;
                     issue_mma(a_lo, b_lo, sf, 0, d_col, kt != 0 ? 1u : 0u);
+                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
+                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
+                    tcgen05_commit_pair(&empty[s], 3);
                     if (more) {
                         stage_wait(s_next, ph_next);
                     }
-                    issue_mma(a_lo, b_lo, sf, 1, d_col, 1u);
-                    if (more) {
-                        stage_copy_sfa(it + 1, s_next);
-                    }
-                    issue_mma(a_lo, b_lo, sf, 2, d_col, 1u);
-                    if (more) {
-                        stage_copy_sfb(it + 1, s_next);
-                    }
-                    issue_mma(a_lo, b_lo, sf, 3, d_col, 1u);
-                    tcgen05_commit_pair(&empty[s], 3);
                     s = s_next;
                     ph = ph_next;
                 }
@@ -305,7 +292,21 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             fence_proxy_async_shared();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive_cluster(map_to_cta(smem_u32(&full[s]), 0));
+                // Both CTAs report their atoms to the leader; the leader's scale loader then copies both CTAs'
+                // atoms into both CTAs' tensor memory (one cta_group::2 copy does the same offsets in the two) and
+                // its commit is the third arrival on the leader's full barrier.  The MMA issuer copies nothing:
+                // a thread gets a tcgen05 instruction out only every ~70 cycles.
+                mbar_arrive_cluster(map_to_cta(smem_u32(&atoms_written[s]), 0));
+                if (cta == 0) {
+                    mbar_wait_cluster(&atoms_written[s], ph, p.status, 207, s);
+                    tcgen05_fence_after();
+                    const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
+                    const uint32_t sf_t = tmem_base + S::kSfCol + s * S::kSfSetCols;
+                    tcgen05_cp_sf_pair_lohi(sf_t, smem_u32(sfa) >> 4, hi_sf);
+                    tcgen05_cp_sf_pair_lohi(sf_t + 4, smem_u32(sfb) >> 4, hi_sf);
+                    tcgen05_cp_sf_pair_lohi(sf_t + 8, (smem_u32(sfb) >> 4) + (512u >> 4), hi_sf);
+                    tcgen05_commit_pair(&full[s], 1);
+                }
             }
             if (has_next) {
 #pragma unroll
@@ -335,13 +336,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t row = m0 + q * 32 + lane;
             for (uint32_t ci = 0; ci < kChunks; ++ci) {
                 uint32_t chunk = ci;
-                if (acc == 0) {
-                    chunk = (ci == 0) ? (kChunks - 1) : ci - 1;  // the shared columns first
+                if (acc == 0) {  // the shared columns first
+                    chunk = ci < S::kOverlapChunks ? kChunks - S::kOverlapChunks + ci : ci - S::kOverlapChunks;
                 }
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + d_col + chunk * 32u, r);
                 tmem_ld_wait();
-                if (ci == 0) {
+                if (ci == S::kOverlapChunks - 1) {
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) {
