@@ -34,7 +34,7 @@ UNIT = "TFLOP/s"
 FP8_NOMINAL_TFLOPS = 4500.0
 NVLINK_NOMINAL_GBS = 900.0
 # dram bytes per launch of the dominant kernel, from the committed ncu summary (profiles/); None = not captured
-GEMM_DRAM_TRAFFIC_BYTES_N1 = 31.83e6  # profiles/mx_gemm_kernel_fused_c3_prefill_n1.md
+GEMM_DRAM_TRAFFIC_BYTES_N1 = 24.69e6  # profiles/mx_gemm_kernel_splitk_c3_prefill_n1.md (dram read + write of one launch)
 
 
 def read_peaks():
