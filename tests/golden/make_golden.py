@@ -19,7 +19,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: GEN_DATA_QUANT_BACKEND=native python tests/golden/make_golden.py /path/to/reference")
+REF = sys.argv[1]
 sys.path.insert(0, os.path.join(REF, "examples", "utils"))
 import gen_mx_quant_allgather_data as ref  # noqa: E402
 
