@@ -15,16 +15,19 @@
 // One CTA per 128 x BLOCK_N output tile, persistent over tiles, 320 threads:
 //   warps 0-3 epilogue: tcgen05.ld of the fp32 accumulator, convert, 16-byte global stores
 //   warp 4    TMA producer: A and B tiles (128-byte swizzle) into a ring of shared-memory stages
-//   warp 5    MMA issuer: tcgen05.cp of the scale atoms into tensor memory, then four
-//             tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per stage
+//   warp 5    MMA issuer: four tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) and one
+//             tcgen05.commit per stage, nothing else (see the scale loaders)
 //   warps 6-9 scale loaders: warp j serves every fourth K tile; plain global loads of the E8M0
 //             bytes (the next K tile's loads are in flight while the current one is stored),
-//             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects
+//             written to shared memory in the 32x16-byte atom layout tcgen05.cp expects, copied into
+//             the stage's scale set in tensor memory by lane 0 (tcgen05.cp), whose tcgen05.commit on the
+//             stage's full barrier is the warp's arrival
 //
-// With FUSED_QUANT the CTA carries fourteen more warps (10-23): six pusher warps, and eight that run the quantise-and-push producer
-// (mx_quant.cuh) on this rank's bf16 shard: quantise, store to every rank's stage over NVLink, publish
-// flags.  The GEMM warps of the same launch (and of the peers' launches) consume behind them, so the
-// quantisation, the allgather and the matmul are one kernel.
+// With FUSED_QUANT the CTA carries fourteen more warps (10-23): eight run the quantise producer (mx_quant.cuh)
+// on this rank's bf16 shard into the local stage and publish local flags, six are pushers that copy finished
+// work items to the peers' stages over NVLink and set the peers' flags.  The GEMM warps of the same launch
+// (and of the peers' launches) consume behind them, so the quantisation, the allgather and the matmul are one
+// kernel.
 //
 // When `flags` is set, a tile is not touched before every (source rank, 16-row chunk) under its
 // rows has been published with the current epoch by the quantise-and-push kernel; tiles are
@@ -301,11 +304,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else if (warp == 5) {
         // ------------------------------- MMA issuer ---------------------------------------
-        // The tensor pipe accepts only a couple of MMAs ahead of the one it is executing, so whatever
-        // this thread does between the last MMA of a K tile and the first of the next is idle time for
-        // the pipe.  The loop therefore looks one K tile ahead: after the first two MMAs of a K tile
-        // are queued it waits for the next stage and copies its scale atoms (into the other of two
-        // scale-factor sets in tensor memory), and only then queues the last two MMAs.
+        // One thread gets a tcgen05 instruction out only every ~70 cycles, so this thread issues what nobody
+        // else can (the MMAs, and the commit that releases the stage) and nothing more: four MMAs of 128 cycles
+        // each leave it enough time for the commit, the wait for the next stage and its address arithmetic.
         if (lane == 0) {
             const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR) | (p.a_e5m2 ? (1u << 7) : 0u) |
                                    (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1

@@ -7,7 +7,10 @@
 // each CTA ends up with the accumulator of its own 128 rows x 256 columns in its own tensor memory.
 // Every CTA loads its own tiles with plain TMA (no cluster multicast anywhere); what crosses the pair is
 // only barrier traffic:
-//   full[s]                     lives in the leader; both CTAs' TMA bytes and scale-loader arrivals go there
+//   full[s]                     lives in the leader; both CTAs' TMA bytes go there, and the commit behind the
+//                               leader's scale copies (tcgen05.cp.cta_group::2 reads the atoms of both CTAs)
+//   atoms_written[s]            lives in the leader; both CTAs' scale loaders arrive once their atoms are in
+//                               shared memory
 //   empty[s], tmem_full[a]      live in each CTA; the leader's tcgen05.commit arrives on both copies
 //   tmem_empty[a], overlap_free[a]  live in the leader; the epilogue warps of both CTAs arrive there
 #pragma once
@@ -150,8 +153,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else if (warp == 5) {
         // ------------------------------- MMA issuer (leader CTA only) ---------------------
-        // Same look-ahead as the single-CTA kernel: the next stage is awaited and its scale atoms copied
-        // between the second and third MMA of the current K tile.
+        // As in the single-CTA kernel the issuer issues the MMAs and the stage-releasing commit, nothing else.
         if (cta == 0 && lane == 0) {
             const uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, true) | (p.a_e5m2 ? (1u << 7) : 0u) |
                                    (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
