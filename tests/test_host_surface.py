@@ -32,6 +32,53 @@ def test_drivers_reject_bad_arguments(host_bins):
     assert r.returncode == 1 and "Invalid arguments" in r.stderr
 
 
+def test_batch_driver_rejects_bad_arguments(host_bins, tmp_path):
+    exe = os.path.join(host_bins, "dynamic_tiling")
+    r = subprocess.run([exe, "a5fp8mxagmm", "1", "1", "0"], capture_output=True, text=True, timeout=60)
+    assert r.returncode != 0 and "Invalid command line options" in r.stderr
+    csv = tmp_path / "shapes.csv"
+    csv.write_text("M,K,N,Transpose A,Transpose B\n256,1024,1024,0,0\n")
+    r = subprocess.run([exe, "no_such_kernel", "1", "1", "0", "tcp://127.0.0.1:8791", "0", "0", "0", "0", "1", str(tmp_path),
+                        str(csv), "1", "1"], capture_output=True, text=True, timeout=60)
+    assert r.returncode != 0 and "not part of this library" in r.stderr
+
+
+@pytest.mark.gpu
+def test_batch_driver_single_rank(host_bins, oracle, cuda, tmp_path):
+    # the reference's batch driver command line (tests/dynamic_tiling): a CSV of shapes, warm-up and timed launches
+    # through KernelDispatcher, one line per shape in output/tiling/tilingData_<time>.csv
+    exe = os.path.join(host_bins, "dynamic_tiling")
+    m, k, n = 256, 1024, 1024
+    cfg = workloads.Config("t", m, k, n, (1,), "normal", "")
+    ac, asc = oracle.quantize_rows(workloads.activation_bits(cfg, 0, seed=4))
+    bc, bsc = oracle.quantize_weight(workloads.weight_bits(cfg, 0, seed=4))
+    data = tmp_path / "data"
+    data.mkdir()
+    ac.tofile(data / "input_a_0.bin")
+    asc.tofile(data / "input_a_scale_0.bin")
+    bc.tofile(data / "input_b_0.bin")
+    bsc.tofile(data / "input_b_scale_0.bin")
+    csv = tmp_path / "shapes.csv"
+    csv.write_text("M,K,N,Transpose A,Transpose B\n8,8,8,0,0\n%d,%d,%d,0,0\n" % (m, k, n))
+    r = subprocess.run([exe, "a5fp8mxagmm", "1", "1", "0", "tcp://127.0.0.1:8792", "0", "0", "0", "1", "1", str(tmp_path),
+                        str(csv), "2", "5", "0", str(data)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "[ERROR]" not in r.stdout and "cudaError:" not in r.stderr, r.stdout + r.stderr
+    out = workloads.bf16_bits_to_f32(np.fromfile(data / "output_0.bin", dtype=np.uint16).reshape(m, n))
+    gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
+    bad, maxdiff = oracle.check_close(out, gold, 1e-2, 1e-3)
+    assert bad == 0, (bad, maxdiff)
+    files = os.listdir(tmp_path / "output" / "tiling")
+    assert len(files) == 1
+    rows = (tmp_path / "output" / "tiling" / files[0]).read_text().strip().splitlines()
+    assert len(rows) == 2 and rows[1].startswith("Ascend950Fp8MxAllGatherMatmul,%d,%d,%d,0,0," % (m, k, n))
+    assert float(rows[1].split(",")[-1]) > 0.0
+    # the quantiser over several shapes, timing only (no data directory: the operator fills its input itself)
+    csv.write_text("M,K,N,Transpose A,Transpose B\n190,1,1024,0,0\n1024,1,7168,0,0\n")
+    r = subprocess.run([exe, "mxqtag", "36", "1", "0", "tcp://127.0.0.1:8793", "0", "0", "0", "0", "2", str(tmp_path),
+                        str(csv), "2", "5"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("cudaStreamSynchronize success") == 2, r.stdout + r.stderr
+
+
 @pytest.mark.gpu
 def test_quant_driver_files_single_rank(host_bins, oracle, cuda, tmp_path):
     m, n = 190, 1024  # ragged M, as in the reference's test_shapes.csv (8190 = 63 * 128 + 126)
