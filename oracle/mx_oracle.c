@@ -12,6 +12,8 @@
  *   - include/catccos/comm/block/comm_block_mx_quant.hpp:413-523,569-664 (ComputeMxQuant,
  *     FP8 branch: exponent-field max, shared exponent, reciprocal scale, clamp, CAST_RINT)
  *                                                               -> mode MXO_MODE_DEVICE
+ *   - examples/utils/gen_mx_quant_allgather_data.py:48-52 and comm_block_mx_quant.hpp:75-76,410 (the E5M2
+ *     output type: emax 15, max 57344)                          -> mxo_quantize_rows_e5m2
  *   - examples/utils/gen_data_fp8_mx_allgather_matmul.py:643-658 (golden GEMM: rank-order
  *     concat of dequantised A times dequantised B, fp32) and :650-656 (B scale file layout
  *     [K/64, N, 2]).
