@@ -268,6 +268,94 @@ void mxo_dequant_rows_e5m2(const uint8_t* codes, const uint8_t* scales, size_t r
     }
 }
 
+/* ---- FP4 E2M1 (the reference's fp4 variant of the same operators: emax 2, max 6;
+ * gen_mx_quant_allgather_data.py:55-62,349-397,413-452; comm_block_mx_quant.hpp:69-70,525-568).  Oracle and
+ * fixtures only: no CUDA kernel reads these yet. ------------------------------------------------------- */
+
+static const float kE2M1[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+
+/* E2M1 code (4 bits: sign, two exponent bits, one mantissa bit) -> fp32. */
+float mxo_e2m1_to_f32(uint8_t c)
+{
+    float v = kE2M1[c & 7];
+    return (c & 8) ? -v : v;
+}
+
+/* fp32 (finite, callers clamp to +-6) -> E2M1 code.
+ * ties_to_zero = 1: the golden's rule, nearest table entry with the smaller index winning a tie
+ *                   (gen_mx_quant_allgather_data.py:383-397): ties go toward zero and every zero is +0.
+ * ties_to_zero = 0: round to nearest even with the sign kept (CAST_RINT on the device,
+ *                   comm_block_mx_quant.hpp:538-555; cvt.rn.satfinite.e2m1x2.f32 on a GPU). */
+uint8_t mxo_e2m1_from_f32(float v, int ties_to_zero)
+{
+    float a = fabsf(v);
+    if (a > 6.0f) {
+        a = 6.0f;
+    }
+    int best = 0;
+    for (int i = 1; i < 8; ++i) {
+        float d = fabsf(a - kE2M1[i]), db = fabsf(a - kE2M1[best]);
+        if (d < db) {
+            best = i;
+        } else if (d == db && !ties_to_zero && (i & 1) == 0) {
+            best = i; /* a tie between neighbours: the even code wins under round-to-nearest-even */
+        }
+    }
+    if (ties_to_zero) {
+        return (uint8_t)((v < 0.0f && best != 0) ? (best | 8) : best);
+    }
+    return (uint8_t)(signbit(v) ? (best | 8) : best);
+}
+
+/* x bf16 [rows, K] -> packed codes [rows, K/2] (low nibble = even column, _pack_fp4_nibbles :400-411) and
+ * scales [rows, K/32].  mode MXO_MODE_GOLDEN: golden rounding and tiny-block rule; MXO_MODE_DEVICE: RNE,
+ * byte = max(E - 2, 0).  K % 32 == 0. */
+int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* packed, uint8_t* scales, int mode)
+{
+    if (K % MXO_BLOCK != 0) {
+        return -1;
+    }
+    size_t nb = K / MXO_BLOCK;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t r = 0; r < (ptrdiff_t)rows; ++r) {
+        for (size_t b = 0; b < nb; ++b) {
+            const uint16_t* xb = x + (size_t)r * K + b * MXO_BLOCK;
+            uint8_t s;
+            float mul = 0.0f;
+            int kind = mxo_block_scale_fmt(xb, 1, mode, 2, &s, &mul);
+            scales[(size_t)r * nb + b] = s;
+            for (int i = 0; i < MXO_BLOCK; i += 2) {
+                uint8_t c[2];
+                for (int j = 0; j < 2; ++j) {
+                    if (kind == 2) {
+                        c[j] = 0x7; /* no NaN in E2M1: the largest magnitude stands in (no reference test pins it) */
+                    } else if (kind == 1) {
+                        c[j] = (uint8_t)((mode == MXO_MODE_GOLDEN) ? 0 : ((xb[i + j] >> 12) & 8));
+                    } else {
+                        c[j] = mxo_e2m1_from_f32(bf16_to_f32(xb[i + j]) * mul, mode == MXO_MODE_GOLDEN);
+                    }
+                }
+                packed[(size_t)r * (K / 2) + (b * MXO_BLOCK + i) / 2] = (uint8_t)(c[0] | (c[1] << 4));
+            }
+        }
+    }
+    return 0;
+}
+
+/* packed E2M1 codes [rows, K/2] + scales [rows, K/32] -> fp32 [rows, K]. */
+void mxo_dequant_rows_e2m1(const uint8_t* packed, const uint8_t* scales, size_t rows, size_t K, float* out)
+{
+    size_t nb = K / MXO_BLOCK;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t r = 0; r < (ptrdiff_t)rows; ++r) {
+        for (size_t k = 0; k < K; ++k) {
+            uint8_t byte = packed[(size_t)r * (K / 2) + k / 2];
+            uint8_t c = (k & 1) ? (byte >> 4) : (byte & 15);
+            out[(size_t)r * K + k] = mxo_e2m1_to_f32(c) * mxo_e8m0_to_f32(scales[(size_t)r * nb + k / MXO_BLOCK]);
+        }
+    }
+}
+
 /* Quantise along the last axis: x bf16 [rows, K] -> codes [rows, K], scales [rows, K/32]
  * (row-major).  K % 32 == 0 (mx_quant_allgather_host.h:21-25).  Returns 0, or -1 on a bad shape. */
 int mxo_quantize_rows(const uint16_t* x, size_t rows, size_t K, uint8_t* codes, uint8_t* scales, int mode)

@@ -68,6 +68,14 @@ def lib() -> ctypes.CDLL:
         L.mxo_e5m2_from_f32.restype = ctypes.c_uint8
         L.mxo_e5m2_to_f32.argtypes = [ctypes.c_uint8]
         L.mxo_e5m2_to_f32.restype = ctypes.c_float
+        L.mxo_quantize_rows_e2m1.argtypes = [vp, sz, sz, vp, vp, ci]
+        L.mxo_quantize_rows_e2m1.restype = ci
+        L.mxo_dequant_rows_e2m1.argtypes = [vp, vp, sz, sz, vp]
+        L.mxo_dequant_rows_e2m1.restype = None
+        L.mxo_e2m1_from_f32.argtypes = [ctypes.c_float, ci]
+        L.mxo_e2m1_from_f32.restype = ctypes.c_uint8
+        L.mxo_e2m1_to_f32.argtypes = [ctypes.c_uint8]
+        L.mxo_e2m1_to_f32.restype = ctypes.c_float
         _lib = L
     return _lib
 
@@ -106,6 +114,28 @@ def quantize_rows(x_bits: np.ndarray, mode: int = MODE_GOLDEN, fmt: int = FMT_E4
     if fn(_p(x_bits), rows, K, _p(codes), _p(scales), mode) != 0:
         raise ValueError("K must be a multiple of 32")
     return codes, scales
+
+
+def quantize_rows_e2m1(x_bits: np.ndarray, mode: int = MODE_GOLDEN):
+    """bf16 bits [rows, K] -> (packed E2M1 codes uint8 [rows, K/2], low nibble = even column; scales [rows, K/32]).
+
+    The FP4 variant of the operators; oracle and fixtures only, no CUDA kernel reads these yet."""
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    rows, K = x_bits.shape
+    packed = np.empty((rows, K // 2), np.uint8)
+    scales = np.empty((rows, K // 32), np.uint8)
+    if lib().mxo_quantize_rows_e2m1(_p(x_bits), rows, K, _p(packed), _p(scales), mode) != 0:
+        raise ValueError("K must be a multiple of 32")
+    return packed, scales
+
+
+def dequant_rows_e2m1(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    rows, half = packed.shape
+    out = np.empty((rows, 2 * half), np.float32)
+    lib().mxo_dequant_rows_e2m1(_p(packed), _p(scales), rows, 2 * half, _p(out))
+    return out
 
 
 def quantize_weight(b_bits: np.ndarray, mode: int = MODE_GOLDEN):

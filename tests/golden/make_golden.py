@@ -144,6 +144,20 @@ def main():
     e5["agmm_golden"] = torch.matmul(torch.cat(a5_deq, dim=0), b_deq).numpy().astype(np.float32)
     save("quant_e5m2.npz", **e5)
 
+    # 6. the FP4 output type (E2M1: emax 2, max 6, two codes per byte), as gen_data_fp4_e2m1 builds its files:
+    #    table rounding, nibble packing, E8M0 scale bytes.  Also on the dequantised tensor, which is what the
+    #    reference feeds its kernel (the two rounding rules agree there).
+    e4 = {}
+    for tag, xin in (("normal", x), ("outlier", xo), ("edges", xe)):
+        xf = torch.from_numpy(bits_f32(xin).copy())
+        q, scale, deq = ref._quantize(xf, "E2M1", 1)
+        _, idx = ref._quantize_to_fp4_lut(q, "E2M1")
+        e4["x_" + tag] = xin
+        e4["packed_" + tag] = ref._pack_fp4_nibbles(idx).numpy().copy()
+        e4["scales_" + tag] = scale.to(torch.float8_e8m0fnu).view(torch.uint8).numpy().copy()[:, : xin.shape[1] // 32]
+        e4["dequant_" + tag] = deq.numpy().astype(np.float32)
+    save("quant_e2m1.npz", **e4)
+
 
 if __name__ == "__main__":
     main()

@@ -116,6 +116,52 @@ def test_e5m2_codec_round_trip(oracle):
     assert L.mxo_e5m2_from_f32(-1e-9) == 0x80
 
 
+# ---- FP4 E2M1 output type: oracle and fixtures only (no CUDA kernel reads them yet) ----
+
+@pytest.mark.parametrize("tag", ["normal", "outlier", "edges"])
+def test_e2m1_quantise_matches_reference_golden(oracle, golden, tag):
+    d = golden("quant_e2m1")
+    packed, scales = oracle.quantize_rows_e2m1(d["x_" + tag])
+    assert np.array_equal(scales, d["scales_" + tag])
+    assert np.array_equal(packed, d["packed_" + tag])
+    deq = oracle.dequant_rows_e2m1(packed, scales)
+    assert np.array_equal(deq, d["dequant_" + tag])
+
+
+def test_e2m1_rounding_rules_agree_on_dequantised_input(oracle, golden):
+    # the golden breaks ties toward zero, the device rounds to nearest even; the reference feeds its kernel the
+    # dequantised tensor (gen_mx_quant_allgather_data.py:529-534), on which both rules give the same codes
+    d = golden("quant_e2m1")
+    deq_bits = workloads.f32_to_bf16_bits(d["dequant_normal"])
+    g_c, g_s = oracle.quantize_rows_e2m1(deq_bits, oracle.MODE_GOLDEN)
+    d_c, d_s = oracle.quantize_rows_e2m1(deq_bits, oracle.MODE_DEVICE)
+    assert np.array_equal(g_s, d["scales_normal"]) and np.array_equal(d_s, g_s)
+    # the golden writes +0 for every zero, the device keeps the sign: compare magnitudes
+    assert np.array_equal(g_c & 0x77, d_c & 0x77)
+    assert np.array_equal(g_c, d["packed_normal"])
+    # on the raw input the two rules differ on ties only
+    r_g, _ = oracle.quantize_rows_e2m1(d["x_normal"], oracle.MODE_GOLDEN)
+    r_d, _ = oracle.quantize_rows_e2m1(d["x_normal"], oracle.MODE_DEVICE)
+    assert 0 < np.count_nonzero((r_g & 0x77) != (r_d & 0x77)) < r_g.size // 4
+
+
+def test_e2m1_codec(oracle):
+    L = oracle.lib()
+    values = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    for code in range(16):
+        v = L.mxo_e2m1_to_f32(code)
+        assert abs(v) == values[code & 7] and (v <= 0 if code & 8 else v >= 0)
+        if code != 8:  # -0 is never written by the golden
+            assert L.mxo_e2m1_from_f32(v, 1) == code
+        assert L.mxo_e2m1_from_f32(v, 0) == code
+    # ties: golden toward zero, device to the even code
+    for x, toward_zero, even in ((0.75, 1, 2), (1.75, 3, 4), (3.5, 5, 6), (0.25, 0, 0), (1.25, 2, 2), (2.5, 4, 4), (5.0, 6, 6)):
+        assert L.mxo_e2m1_from_f32(x, 1) == toward_zero and L.mxo_e2m1_from_f32(x, 0) == even
+        assert L.mxo_e2m1_from_f32(-x, 0) == even | 8
+    assert L.mxo_e2m1_from_f32(100.0, 0) == 7 and L.mxo_e2m1_from_f32(-100.0, 1) == 15
+    assert L.mxo_e2m1_from_f32(-0.1, 1) == 0 and L.mxo_e2m1_from_f32(-0.1, 0) == 8
+
+
 def test_workload_shapes_and_determinism():
     cfg = workloads.CONFIGS["c4_outlier"]
     a = workloads.activation_bits(cfg, 2, seed=0, rows=8)
