@@ -24,6 +24,7 @@ EXPORTS = [
     "catccos_b200_fp8_mx_allgather_matmul",
     "catccos_b200_mx_quant_allgather_matmul",
     "catccos_b200_mx_quant",
+    "catccos_b200_mx_quant_fp4",
     "catccos_b200_mx_gemm",
     "catccos_b200_mx_quant_matmul_static",
     "catccos_b200_transpose_weight",
@@ -78,6 +79,7 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_fp8_mx_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant.argtypes = [vp, vp, u32, u32, vp, vp]
+    L.catccos_b200_mx_quant_fp4.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_gemm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_mx_quant_matmul_static.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_transpose_weight.argtypes = [vp, vp, vp, u32, u32]
@@ -171,6 +173,19 @@ def mx_quant(x_bf16):
     _check("catccos_b200_mx_quant",
            load().catccos_b200_mx_quant(_stream(), x_bf16.data_ptr(), rows, k, codes.data_ptr(), scales.data_ptr()))
     return codes, scales
+
+
+def mx_quant_fp4(x_bf16):
+    """bf16 [rows, K] -> (packed E2M1 codes uint8 [rows, K/2], scales uint8 [rows, K/32]); no communication."""
+    import torch
+
+    rows, k = x_bf16.shape
+    assert x_bf16.is_cuda and x_bf16.is_contiguous() and x_bf16.element_size() == 2
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x_bf16.device)
+    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=x_bf16.device)
+    _check("catccos_b200_mx_quant_fp4",
+           load().catccos_b200_mx_quant_fp4(_stream(), x_bf16.data_ptr(), rows, k, packed.data_ptr(), scales.data_ptr()))
+    return packed, scales
 
 
 def mx_gemm(a_codes, a_scales, b, b_scales, out=None, out_dtype=None):

@@ -1042,6 +1042,29 @@ int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint
     return launch_quant_push(rc, (cudaStream_t)stream, q, false, true);
 }
 
+int catccos_b200_mx_quant_fp4(void* stream, const void* in_bf16, uint32_t rows, uint32_t k, void* packed, void* scales)
+{
+    if (!in_bf16 || !packed || !scales || rows == 0 || k == 0 || k % 32 != 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    if (((uintptr_t)in_bf16 & 15u) || ((uintptr_t)packed & 7u)) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    RankCtx& rc = cur();
+    const uint32_t rows_per_cta = kQuantThreads / 32;
+    uint32_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
+    const uint32_t cap = (uint32_t)rc.num_sms * 6u;
+    if (grid > cap) grid = cap;
+    mx_quant_e2m1_kernel<<<grid, kQuantThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const uint16_t*>(in_bf16), rows, k, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales),
+        g.tiny_block_rule != 0 ? 1u : 0u);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
 int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out_codes, void* out_scales, void* symm,
                                     const catccos_b200_tiling_t* t, uint32_t magic)
 {

@@ -14,6 +14,8 @@
 //   in mode kQuantDeviceTiny, the reference device kernel (byte = max(E - 8, 0)).  Inf/NaN blocks: 0xFF / 0x7F.
 #pragma once
 
+#include <cuda_fp4.h>
+
 #include "common.cuh"
 
 namespace catccos {
@@ -447,6 +449,56 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
             }
         }
         __syncthreads();
+    }
+}
+
+// bf16 [rows, K] -> FP4 E2M1 codes, two per byte (low nibble = even column), + one E8M0 scale per 32 elements.
+// The FP4 branch of the reference's quantiser (include/catccos/comm/block/comm_block_mx_quant.hpp:525-568, emax
+// constant block_epilogue_dynamic_mx_quant.hpp:53): the same exponent rule with emax 2, saturation at +-6,
+// round to nearest even (cvt.rn.satfinite.e2m1x2.f32).  A warp takes a row; a lane quantises 16 consecutive
+// values per 512-column step (two lanes share a 32-block) and stores 8 bytes of codes.
+__global__ void __launch_bounds__(kQuantThreads) mx_quant_e2m1_kernel(const uint16_t* __restrict__ in, uint32_t rows, uint32_t K,
+                                                                      uint8_t* __restrict__ packed,
+                                                                      uint8_t* __restrict__ scales, uint32_t device_tiny)
+{
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sf_cols = K / 32;
+    for (uint32_t row = blockIdx.x * (kQuantThreads / 32) + warp; row < rows; row += gridDim.x * (kQuantThreads / 32)) {
+        for (uint32_t cb = 0; cb < K; cb += kQuantColsPerWarpStep) {
+            const uint32_t col = cb + lane * 16;
+            const bool ok = col < K;
+            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+            if (ok) {
+                const uint4* src = reinterpret_cast<const uint4*>(in + (size_t)row * K + col);
+                v0 = __ldcs(src);
+                v1 = __ldcs(src + 1);
+            }
+            uint32_t amax = max(absmax_bits8(v0), absmax_bits8(v1));
+            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+            uint32_t byte;
+            float mul;
+            bool nonfinite;
+            block_scale(amax, device_tiny != 0u, 2u, byte, mul, nonfinite);
+            const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            uint32_t o[2] = {0u, 0u};
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) {
+                const float lo = __uint_as_float(w[i] << 16) * mul, hi = __uint_as_float(w[i] & 0xFFFF0000u) * mul;
+                const uint32_t b = __nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+                o[i >> 2] |= (b & 0xFFu) << (8u * (i & 3u));
+            }
+            if (nonfinite) {
+                o[0] = o[1] = 0x77777777u;  // E2M1 has no NaN: the largest magnitude stands in
+            } else if (mul == 0.0f && device_tiny == 0u) {
+                o[0] = o[1] = 0u;  // the golden writes +0 for every element of a block below 1e-12
+            }
+            if (ok) {
+                *reinterpret_cast<uint2*>(packed + (size_t)row * (K / 2) + col / 2) = make_uint2(o[0], o[1]);
+                if ((lane & 1u) == 0u) {
+                    scales[(size_t)row * sf_cols + col / 32] = (uint8_t)byte;
+                }
+            }
+        }
     }
 }
 

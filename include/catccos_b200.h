@@ -94,6 +94,13 @@ int catccos_b200_mx_quant_allgather_matmul(void* stream, const void* a_bf16, con
  * bf16 [rows, k] -> codes [rows, k] + scales [rows, k/32], no communication. */
 int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint32_t k, void* codes, void* scales);
 
+/* The FP4 branch of the same quantiser (comm_block_mx_quant.hpp:525-568; the reference's float4_e2m1x2_t output
+ * type, emax 2, +-6): bf16 [rows, k] -> packed E2M1 codes [rows, k/2] (two per byte, low nibble = even column,
+ * as gen_mx_quant_allgather_data.py:400-411 packs them) + scales [rows, k/32].  Round to nearest even, as the
+ * reference's device cast; its CPU golden rounds ties toward zero instead, and the two agree on the dequantised
+ * tensors the reference feeds its kernel.  No communication, and no GEMM reads these codes yet. */
+int catccos_b200_mx_quant_fp4(void* stream, const void* in_bf16, uint32_t rows, uint32_t k, void* packed, void* scales);
+
 /* BlockMmadTla<MmadMx> main loop on data that is already gathered
  * (ascend950_fp8_mx_allgather_matmul_device.h:47-57): c [m, n] = dequant(a)[m, k] x dequant(b)[k, n]. */
 int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,

@@ -156,3 +156,41 @@ def test_e5m2_all_bf16_values(capi, cuda, oracle):
         capi.set_option("a_dtype", 0)
     _assert_bit_exact(got_s, want_s, "scales")
     _assert_bit_exact(got_c, want_c, "codes")
+
+
+# ---- FP4 E2M1 output type (catccos_b200_mx_quant_fp4): round to nearest even, as the reference's device cast ----
+
+def _quant_fp4_gpu(capi, torch, bits):
+    packed, scales = capi.mx_quant_fp4(to_dev_bf16(torch, np.ascontiguousarray(bits)))
+    torch.cuda.synchronize()
+    return packed.cpu().numpy(), scales.cpu().numpy()
+
+
+def test_fp4_matches_reference_golden_on_dequantised_input(capi, cuda, golden):
+    # the reference feeds its kernel the dequantised tensor (gen_mx_quant_allgather_data.py:529-534): there the
+    # device's rounding and the golden's table rounding agree, and the golden fixture is the expected output
+    d = golden("quant_e2m1")
+    for tag in ("normal", "outlier"):
+        bits = workloads.f32_to_bf16_bits(d["dequant_" + tag])
+        packed, scales = _quant_fp4_gpu(capi, cuda, bits)
+        _assert_bit_exact(scales, d["scales_" + tag], "scales " + tag)
+        _assert_bit_exact(packed, d["packed_" + tag], "codes " + tag)
+
+
+@pytest.mark.parametrize("rows,k", [(1, 32), (17, 160), (130, 1056), (5, 7168)])
+def test_fp4_matches_oracle_device_rule(capi, cuda, oracle, golden, rows, k):
+    rng = np.random.default_rng(rows * 7919 + k)
+    x = workloads.f32_to_bf16_bits(rng.standard_normal((rows, k), dtype=np.float32) * np.float32(2.0))
+    capi.set_option("tiny_block_rule", 1)
+    try:
+        want_c, want_s = oracle.quantize_rows_e2m1(x, oracle.MODE_DEVICE)
+        got_c, got_s = _quant_fp4_gpu(capi, cuda, x)
+        _assert_bit_exact(got_s, want_s, "scales")
+        _assert_bit_exact(got_c, want_c, "codes")
+        e = golden("quant_e2m1")["x_edges"]  # zeros, subnormals, tiny blocks, ties, Inf/NaN blocks
+        want_c, want_s = oracle.quantize_rows_e2m1(e, oracle.MODE_DEVICE)
+        got_c, got_s = _quant_fp4_gpu(capi, cuda, e)
+        _assert_bit_exact(got_s, want_s, "edge scales")
+        _assert_bit_exact(got_c, want_c, "edge codes")
+    finally:
+        capi.set_option("tiny_block_rule", 0)
