@@ -41,8 +41,11 @@ static inline float bf16_to_f32(uint16_t b)
     return f;
 }
 
-static inline float pow2i(int e) /* 2^e for e in [-126, 127] as a normal float */
+static inline float pow2i(int e) /* 2^e for e in [-149, 127]; below -126 the result is a subnormal */
 {
+    if (e < -126) {
+        return ldexpf(1.0f, e); /* reached by E1M2 (emax 0): a block maximum of 2^127 is divided by 2^127 */
+    }
     uint32_t u = (uint32_t)(e + 127) << 23;
     float f;
     memcpy(&f, &u, 4);
@@ -273,6 +276,29 @@ void mxo_dequant_rows_e5m2(const uint8_t* codes, const uint8_t* scales, size_t r
  * fixtures only: no CUDA kernel reads these yet. ------------------------------------------------------- */
 
 static const float kE2M1[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+/* E1M2 (one exponent bit, two mantissa bits, bias 1; emax 0, max 1.75; gen_mx_quant_allgather_data.py:63-70) */
+static const float kE1M2[8] = {0.0f, 0.25f, 0.5f, 0.75f, 1.0f, 1.25f, 1.5f, 1.75f};
+
+static uint8_t mxo_fp4_from_f32(const float* table, float v, int ties_to_zero)
+{
+    float a = fabsf(v);
+    if (a > table[7]) {
+        a = table[7];
+    }
+    int best = 0;
+    for (int i = 1; i < 8; ++i) {
+        float d = fabsf(a - table[i]), db = fabsf(a - table[best]);
+        if (d < db) {
+            best = i;
+        } else if (d == db && !ties_to_zero && (i & 1) == 0) {
+            best = i; /* a tie between neighbours: the even code wins under round-to-nearest-even */
+        }
+    }
+    if (ties_to_zero) {
+        return (uint8_t)((v < 0.0f && best != 0) ? (best | 8) : best);
+    }
+    return (uint8_t)(signbit(v) ? (best | 8) : best);
+}
 
 /* E2M1 code (4 bits: sign, two exponent bits, one mantissa bit) -> fp32. */
 float mxo_e2m1_to_f32(uint8_t c)
@@ -288,29 +314,25 @@ float mxo_e2m1_to_f32(uint8_t c)
  *                   comm_block_mx_quant.hpp:538-555; cvt.rn.satfinite.e2m1x2.f32 on a GPU). */
 uint8_t mxo_e2m1_from_f32(float v, int ties_to_zero)
 {
-    float a = fabsf(v);
-    if (a > 6.0f) {
-        a = 6.0f;
-    }
-    int best = 0;
-    for (int i = 1; i < 8; ++i) {
-        float d = fabsf(a - kE2M1[i]), db = fabsf(a - kE2M1[best]);
-        if (d < db) {
-            best = i;
-        } else if (d == db && !ties_to_zero && (i & 1) == 0) {
-            best = i; /* a tie between neighbours: the even code wins under round-to-nearest-even */
-        }
-    }
-    if (ties_to_zero) {
-        return (uint8_t)((v < 0.0f && best != 0) ? (best | 8) : best);
-    }
-    return (uint8_t)(signbit(v) ? (best | 8) : best);
+    return mxo_fp4_from_f32(kE2M1, v, ties_to_zero);
+}
+
+float mxo_e1m2_to_f32(uint8_t c)
+{
+    float v = kE1M2[c & 7];
+    return (c & 8) ? -v : v;
+}
+
+uint8_t mxo_e1m2_from_f32(float v, int ties_to_zero)
+{
+    return mxo_fp4_from_f32(kE1M2, v, ties_to_zero);
 }
 
 /* x bf16 [rows, K] -> packed codes [rows, K/2] (low nibble = even column, _pack_fp4_nibbles :400-411) and
  * scales [rows, K/32].  mode MXO_MODE_GOLDEN: golden rounding and tiny-block rule; MXO_MODE_DEVICE: RNE,
  * byte = max(E - 2, 0).  K % 32 == 0. */
-int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* packed, uint8_t* scales, int mode)
+static int mxo_quantize_rows_fp4(const float* table, int emax, const uint16_t* x, size_t rows, size_t K, uint8_t* packed,
+                                 uint8_t* scales, int mode)
 {
     if (K % MXO_BLOCK != 0) {
         return -1;
@@ -322,7 +344,7 @@ int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* pa
             const uint16_t* xb = x + (size_t)r * K + b * MXO_BLOCK;
             uint8_t s;
             float mul = 0.0f;
-            int kind = mxo_block_scale_fmt(xb, 1, mode, 2, &s, &mul);
+            int kind = mxo_block_scale_fmt(xb, 1, mode, emax, &s, &mul);
             scales[(size_t)r * nb + b] = s;
             for (int i = 0; i < MXO_BLOCK; i += 2) {
                 uint8_t c[2];
@@ -332,7 +354,7 @@ int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* pa
                     } else if (kind == 1) {
                         c[j] = (uint8_t)((mode == MXO_MODE_GOLDEN) ? 0 : ((xb[i + j] >> 12) & 8));
                     } else {
-                        c[j] = mxo_e2m1_from_f32(bf16_to_f32(xb[i + j]) * mul, mode == MXO_MODE_GOLDEN);
+                        c[j] = mxo_fp4_from_f32(table, bf16_to_f32(xb[i + j]) * mul, mode == MXO_MODE_GOLDEN);
                     }
                 }
                 packed[(size_t)r * (K / 2) + (b * MXO_BLOCK + i) / 2] = (uint8_t)(c[0] | (c[1] << 4));
@@ -342,8 +364,19 @@ int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* pa
     return 0;
 }
 
-/* packed E2M1 codes [rows, K/2] + scales [rows, K/32] -> fp32 [rows, K]. */
-void mxo_dequant_rows_e2m1(const uint8_t* packed, const uint8_t* scales, size_t rows, size_t K, float* out)
+int mxo_quantize_rows_e2m1(const uint16_t* x, size_t rows, size_t K, uint8_t* packed, uint8_t* scales, int mode)
+{
+    return mxo_quantize_rows_fp4(kE2M1, 2, x, rows, K, packed, scales, mode);
+}
+
+/* The E1M2 form (emax 0, max 1.75): oracle only. */
+int mxo_quantize_rows_e1m2(const uint16_t* x, size_t rows, size_t K, uint8_t* packed, uint8_t* scales, int mode)
+{
+    return mxo_quantize_rows_fp4(kE1M2, 0, x, rows, K, packed, scales, mode);
+}
+
+static void mxo_dequant_rows_fp4(const float* table, const uint8_t* packed, const uint8_t* scales, size_t rows, size_t K,
+                                 float* out)
 {
     size_t nb = K / MXO_BLOCK;
 #pragma omp parallel for schedule(static)
@@ -351,9 +384,21 @@ void mxo_dequant_rows_e2m1(const uint8_t* packed, const uint8_t* scales, size_t 
         for (size_t k = 0; k < K; ++k) {
             uint8_t byte = packed[(size_t)r * (K / 2) + k / 2];
             uint8_t c = (k & 1) ? (byte >> 4) : (byte & 15);
-            out[(size_t)r * K + k] = mxo_e2m1_to_f32(c) * mxo_e8m0_to_f32(scales[(size_t)r * nb + k / MXO_BLOCK]);
+            float v = table[c & 7];
+            out[(size_t)r * K + k] = ((c & 8) ? -v : v) * mxo_e8m0_to_f32(scales[(size_t)r * nb + k / MXO_BLOCK]);
         }
     }
+}
+
+/* packed E2M1 / E1M2 codes [rows, K/2] + scales [rows, K/32] -> fp32 [rows, K]. */
+void mxo_dequant_rows_e2m1(const uint8_t* packed, const uint8_t* scales, size_t rows, size_t K, float* out)
+{
+    mxo_dequant_rows_fp4(kE2M1, packed, scales, rows, K, out);
+}
+
+void mxo_dequant_rows_e1m2(const uint8_t* packed, const uint8_t* scales, size_t rows, size_t K, float* out)
+{
+    mxo_dequant_rows_fp4(kE1M2, packed, scales, rows, K, out);
 }
 
 /* Quantise along the last axis: x bf16 [rows, K] -> codes [rows, K], scales [rows, K/32]

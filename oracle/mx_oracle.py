@@ -76,6 +76,10 @@ def lib() -> ctypes.CDLL:
         L.mxo_e2m1_from_f32.restype = ctypes.c_uint8
         L.mxo_e2m1_to_f32.argtypes = [ctypes.c_uint8]
         L.mxo_e2m1_to_f32.restype = ctypes.c_float
+        L.mxo_quantize_rows_e1m2.argtypes = [vp, sz, sz, vp, vp, ci]
+        L.mxo_quantize_rows_e1m2.restype = ci
+        L.mxo_dequant_rows_e1m2.argtypes = [vp, vp, sz, sz, vp]
+        L.mxo_dequant_rows_e1m2.restype = None
         _lib = L
     return _lib
 
@@ -135,6 +139,26 @@ def dequant_rows_e2m1(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
     rows, half = packed.shape
     out = np.empty((rows, 2 * half), np.float32)
     lib().mxo_dequant_rows_e2m1(_p(packed), _p(scales), rows, 2 * half, _p(out))
+    return out
+
+
+def quantize_rows_e1m2(x_bits: np.ndarray, mode: int = MODE_GOLDEN):
+    """The E1M2 form of quantize_rows_e2m1 (emax 0, max 1.75); oracle only."""
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    rows, K = x_bits.shape
+    packed = np.empty((rows, K // 2), np.uint8)
+    scales = np.empty((rows, K // 32), np.uint8)
+    if lib().mxo_quantize_rows_e1m2(_p(x_bits), rows, K, _p(packed), _p(scales), mode) != 0:
+        raise ValueError("K must be a multiple of 32")
+    return packed, scales
+
+
+def dequant_rows_e1m2(packed: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    rows, half = packed.shape
+    out = np.empty((rows, 2 * half), np.float32)
+    lib().mxo_dequant_rows_e1m2(_p(packed), _p(scales), rows, 2 * half, _p(out))
     return out
 
 

@@ -158,6 +158,18 @@ def main():
         e4["dequant_" + tag] = deq.numpy().astype(np.float32)
     save("quant_e2m1.npz", **e4)
 
+    # 7. the same for E1M2 (emax 0, max 1.75), the other FP4 type of the generator
+    e1 = {}
+    for tag, xin in (("normal", x), ("edges", xe)):
+        xf = torch.from_numpy(bits_f32(xin).copy())
+        q, scale, deq = ref._quantize(xf, "E1M2", 1)
+        _, idx = ref._quantize_to_fp4_lut(q, "E1M2")
+        e1["x_" + tag] = xin
+        e1["packed_" + tag] = ref._pack_fp4_nibbles(idx).numpy().copy()
+        e1["scales_" + tag] = scale.to(torch.float8_e8m0fnu).view(torch.uint8).numpy().copy()[:, : xin.shape[1] // 32]
+        e1["dequant_" + tag] = deq.numpy().astype(np.float32)
+    save("quant_e1m2.npz", **e1)
+
 
 if __name__ == "__main__":
     main()

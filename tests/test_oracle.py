@@ -162,6 +162,17 @@ def test_e2m1_codec(oracle):
     assert L.mxo_e2m1_from_f32(-0.1, 1) == 0 and L.mxo_e2m1_from_f32(-0.1, 0) == 8
 
 
+@pytest.mark.parametrize("tag", ["normal", "edges"])
+def test_e1m2_quantise_matches_reference_golden(oracle, golden, tag):
+    # the other FP4 type of the reference generator (emax 0, max 1.75): oracle only.  The edge fixture holds a block
+    # whose maximum has exponent 254, which this format divides by 2^127 (a subnormal multiplier)
+    d = golden("quant_e1m2")
+    packed, scales = oracle.quantize_rows_e1m2(d["x_" + tag])
+    assert np.array_equal(scales, d["scales_" + tag])
+    assert np.array_equal(packed, d["packed_" + tag])
+    assert np.array_equal(oracle.dequant_rows_e1m2(packed, scales), d["dequant_" + tag])
+
+
 def test_workload_shapes_and_determinism():
     cfg = workloads.CONFIGS["c4_outlier"]
     a = workloads.activation_bits(cfg, 2, seed=0, rows=8)
