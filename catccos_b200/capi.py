@@ -10,7 +10,10 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcatccos_b200.so")
+# CATCCOS_B200_TRACE=1 in the environment selects the library built with the device-side timeline
+# (python -m catccos_b200.build --trace); everything else is the same C ABI.
+TRACE = os.environ.get("CATCCOS_B200_TRACE", "") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "libcatccos_b200_trace.so" if TRACE else "libcatccos_b200.so")
 
 EXPORTS = [
     "catccos_b200_init",
@@ -27,7 +30,6 @@ EXPORTS = [
     "catccos_b200_mx_quant_fp4",
     "catccos_b200_mx_gemm",
     "catccos_b200_mx_quant_matmul_static",
-    "catccos_b200_transpose_weight",
     "catccos_b200_last_status",
     "catccos_b200_set_option",
     "catccos_b200_launch_count",
@@ -82,7 +84,6 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_mx_quant_fp4.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_gemm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_mx_quant_matmul_static.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32]
-    L.catccos_b200_transpose_weight.argtypes = [vp, vp, vp, u32, u32]
     L.catccos_b200_last_status.argtypes = [ctypes.POINTER(u32)]
     L.catccos_b200_set_option.argtypes = [ctypes.c_char_p, i64]
     L.catccos_b200_launch_count.argtypes = []
@@ -90,6 +91,11 @@ def load() -> ctypes.CDLL:
     for name in EXPORTS:
         if name not in ("catccos_b200_symm_bytes_needed", "catccos_b200_launch_count"):
             getattr(L, name).restype = i32
+    if TRACE:
+        L.catccos_b200_trace_arm.argtypes = []
+        L.catccos_b200_trace_arm.restype = i32
+        L.catccos_b200_trace_read.argtypes = [ctypes.POINTER(ctypes.c_uint64), u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+        L.catccos_b200_trace_read.restype = i32
     _lib = L
     return L
 
@@ -159,6 +165,22 @@ def launch_count() -> int:
     return int(load().catccos_b200_launch_count())
 
 
+def trace_arm() -> None:
+    """Trace build only: the next GEMM launch of the acting rank records its device-side timeline."""
+    _check("catccos_b200_trace_arm", load().catccos_b200_trace_arm())
+
+
+def trace_read():
+    """Trace build only: the armed launch's timeline as a numpy array [CTAs, slots] of uint64."""
+    import numpy as np
+
+    buf = (ctypes.c_uint64 * (256 * 128))()
+    grid, slots = ctypes.c_uint32(), ctypes.c_uint32()
+    _check("catccos_b200_trace_read",
+           load().catccos_b200_trace_read(buf, len(buf), ctypes.byref(grid), ctypes.byref(slots)))
+    return np.frombuffer(buf, dtype=np.uint64, count=grid.value * slots.value).reshape(grid.value, slots.value).copy()
+
+
 # ---------------------------------------------------------------------------------------------
 # operators on torch CUDA tensors
 # ---------------------------------------------------------------------------------------------
@@ -189,7 +211,7 @@ def mx_quant_fp4(x_bf16):
 
 
 def mx_gemm(a_codes, a_scales, b, b_scales, out=None, out_dtype=None):
-    """c [M, N] = dequant(a)[M, K] x dequant(b); b is [K, N] (or [N, K] with option b_layout = 1)."""
+    """c [M, N] = dequant(a)[M, K] x dequant(b [K, N])."""
     import torch
 
     m, k = a_codes.shape
@@ -209,16 +231,6 @@ def mx_quant_matmul_static(a_bf16, b, b_scales, c) -> None:
     _check("catccos_b200_mx_quant_matmul_static",
            load().catccos_b200_mx_quant_matmul_static(_stream(), a_bf16.data_ptr(), b.data_ptr(), b_scales.data_ptr(),
                                                       c.data_ptr(), m, n, k))
-
-
-def transpose_weight(b):
-    import torch
-
-    k, n = b.shape
-    bt = torch.empty((n, k), dtype=torch.uint8, device=b.device)
-    _check("catccos_b200_transpose_weight",
-           load().catccos_b200_transpose_weight(_stream(), b.data_ptr(), bt.data_ptr(), k, n))
-    return bt
 
 
 def mx_quant_allgather(x_bf16, out_codes, out_scales, symm: int, world: int) -> None:

@@ -15,6 +15,7 @@
 
 #include "../../include/catccos_b200.h"
 #include "bootstrap.hpp"
+#include "internal_options.h"
 #include "common.cuh"
 #include "mx_gemm.cuh"
 #include "mx_gemm_pair.cuh"
@@ -112,8 +113,10 @@ struct RankCtx {
     float* splitk_ws = nullptr;
     uint32_t* splitk_flags = nullptr;
     uint32_t splitk_epoch = 0;
-    cudaStream_t side = nullptr;    // the producer kernel runs here, beside the GEMM on the caller's stream
-    cudaEvent_t fork = nullptr, join = nullptr;
+#ifdef CATCCOS_TRACE
+    unsigned long long* trace = nullptr;  // [SMs][kTraceSlots] timeline words of the armed launch
+    int trace_grid = 0;
+#endif
 };
 
 struct SymmAlloc {
@@ -140,22 +143,23 @@ struct State {
     Bootstrap boot;
     Driver drv;
     // options
+    // options a caller may set (include/catccos_b200.h)
     int tiny_block_rule = 0;
     int c_dtype = 0;
-    int b_layout = 0;
+    // test and tuning hooks (internal_options.h)
     int block_n = 0;
     int phase_mask = 3;
-    int publish_scope = 0;   // 0 = automatic (system scope when world > 1), 1 = system, 2 = GPU
-    int quant_items_per_sm = 4;
     int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
-    int group_rows = 0;      // 0 = automatic; else rows per send group (multiple of 16)
-    int push_mode = 0;       // fused kernel: 0 = pusher warps forward the local stage, 1 = quantise warps store to all ranks
-    int fuse_mode = -1;      // -1 = automatic, 0 = quantise warps inside the GEMM kernel, 1 / 2 = two kernels on two
-                             // streams, 3 = (one rank only) quantise kernel, then GEMM kernel, on the caller's stream
+    int fuse_mode = -1;      // -1 = automatic, 0 = quantise warps inside the GEMM kernel, 3 = (one rank only) quantise
+                             // kernel, then GEMM kernel, 4 = quantise kernel, then GEMM-and-push kernel
+    int push_workers = 0;    // 0 = every pusher warp of the grid, else only the first push_workers
     int a_dtype = 0;         // element type of the A codes (what the quantiser writes, what the GEMM reads): 0 = E4M3, 1 = E5M2
     int b_dtype = 0;         // element type of the B codes the caller passes
     int split_k = 0;         // 0 = automatic, 1 = never split K, 2..8 = split K in that many parts when it fits
     uint64_t timeout_ns = 2000ull * 1000000ull;
+#ifdef CATCCOS_TRACE
+    bool trace_armed = false;  // the next GEMM launch of the acting rank writes its timeline
+#endif
     std::vector<uint32_t> local_alloc_cursor;  // local mode: next allocation index per rank
 };
 
@@ -174,11 +178,10 @@ int setup_rank_ctx(RankCtx& rc, int device)
     CUDA_TRY(cudaMalloc(&rc.splitk_flags, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     CUDA_TRY(cudaMemset(rc.splitk_flags, 0, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     rc.splitk_epoch = 0;
-    int lo = 0, hi = 0;
-    CUDA_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    CUDA_TRY(cudaStreamCreateWithPriority(&rc.side, cudaStreamNonBlocking, hi));
-    CUDA_TRY(cudaEventCreateWithFlags(&rc.fork, cudaEventDisableTiming));
-    CUDA_TRY(cudaEventCreateWithFlags(&rc.join, cudaEventDisableTiming));
+#ifdef CATCCOS_TRACE
+    CUDA_TRY(cudaMalloc(&rc.trace, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long)));
+    CUDA_TRY(cudaMemset(rc.trace, 0, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long)));
+#endif
     return 0;
 }
 
@@ -188,9 +191,9 @@ void destroy_rank_ctx(RankCtx& rc)
     if (rc.status) cudaFree(rc.status);
     if (rc.splitk_ws) cudaFree(rc.splitk_ws);
     if (rc.splitk_flags) cudaFree(rc.splitk_flags);
-    if (rc.side) cudaStreamDestroy(rc.side);
-    if (rc.fork) cudaEventDestroy(rc.fork);
-    if (rc.join) cudaEventDestroy(rc.join);
+#ifdef CATCCOS_TRACE
+    if (rc.trace) cudaFree(rc.trace);
+#endif
     rc = RankCtx();
 }
 
@@ -274,16 +277,15 @@ uint32_t quant_mode(bool prequant)
     return prequant ? kQuantPreQuantised : (g.tiny_block_rule != 0 ? kQuantDeviceTiny : kQuantGolden);
 }
 
-uint32_t quant_sys_scope(uint32_t world)
-{
-    return g.publish_scope == 1 ? 1u : (g.publish_scope == 2 ? 0u : (world > 1 ? 1u : 0u));
-}
+uint32_t quant_sys_scope(uint32_t world) { return world > 1 ? 1u : 0u; }
+
+constexpr uint32_t kQuantItemsPerSm = 4;  // work items per SM the quantiser's K-segment choice aims for
 
 void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
 {
     const uint32_t chunks = (M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t max_segs = (K + kQuantColsPerWarpStep - 1) / kQuantColsPerWarpStep;
-    uint32_t want = ((uint32_t)num_sms * (uint32_t)g.quant_items_per_sm + chunks - 1) / chunks;
+    uint32_t want = ((uint32_t)num_sms * kQuantItemsPerSm + chunks - 1) / chunks;
     if (want < 1) want = 1;
     if (want > max_segs) want = max_segs;
     uint32_t seg_cols = (uint32_t)align_up((K + want - 1) / want, kQuantColsPerWarpStep);
@@ -328,11 +330,11 @@ int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t o
     return 0;
 }
 
-template <uint32_t BLOCK_N, bool B_MN, typename OutT, bool FUSED>
+template <uint32_t BLOCK_N, typename OutT, bool FUSED>
 int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                      bool overlap_predecessor)
 {
-    auto kern = mx_gemm_kernel<BLOCK_N, B_MN, OutT, FUSED>;
+    auto kern = mx_gemm_kernel<BLOCK_N, OutT, FUSED>;
     static bool attr_done[kMaxRanks * 2] = {};
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -410,7 +412,6 @@ struct GemmPlan {
 // Tiling of one GEMM launch: CTA pairs or single CTAs, tile width, and the number of K parts.
 GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
 {
-    const bool b_mn = g.b_layout == 0;
     // waves x K-tile period of each candidate (same K for all, so K drops out)
     const uint32_t m128 = (Mg + 127) / 128, m256 = (Mg + 255) / 256;
     const uint32_t n128 = (N + 127) / 128, n256 = (N + 255) / 256;
@@ -420,7 +421,7 @@ GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
     const double t_256 = waves(m128 * n256, sms) * kPeriodSingle256;
     const double t_128 = waves(m128 * n128, sms) * kPeriodSingle128;
     GemmPlan plan;
-    plan.use_pair = b_mn && (g.cta_pair == 1 || (g.cta_pair == 0 && g.block_n == 0 && t_pair < t_256 && t_pair < t_128));
+    plan.use_pair = (g.cta_pair == 1 || (g.cta_pair == 0 && g.block_n == 0 && t_pair < t_256 && t_pair < t_128));
     plan.ksplit = 1;
     uint32_t bn = (uint32_t)g.block_n;
     // Split K when the tiles would leave at least half of the SMs idle: every (tile, K part) pair gets its
@@ -469,10 +470,18 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         ERROR_LOG("mx gemm operands must be 16-byte aligned (the output 32-byte aligned)");
         return CATCCOS_B200_EINVAL;
     }
-    const bool b_mn = g.b_layout == 0;
     const bool f16 = g.c_dtype == 1;
     p.status = rc.status;
     p.timeout_ns = g.timeout_ns;
+    // a barrier inside the kernel may have to wait for as long as the flag wait it depends on
+    p.bar_timeout_ns = 2 * g.timeout_ns + 1000000000ull;
+#ifdef CATCCOS_TRACE
+    if (g.trace_armed && rc.trace != nullptr) {
+        g.trace_armed = false;
+        CUDA_TRY(cudaMemsetAsync(rc.trace, 0, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long), st));
+        p.trace = p.q.trace = p.push.trace = rc.trace;
+    }
+#endif
     p.a_e5m2 = g.a_dtype == 1 ? 1u : 0u;
     p.b_e5m2 = g.b_dtype == 1 ? 1u : 0u;
     const GemmPlan plan = plan_gemm(rc, p.Mg, p.N, p.K);
@@ -487,6 +496,9 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         rc2 = encode_map_2d(&pb, b, p.N, p.K, 128, kGemmBlockK);
         if (rc2 != 0) return rc2;
         const uint32_t tiles = m256 * n256;
+#ifdef CATCCOS_TRACE
+        rc.trace_grid = (int)(2 * std::min(tiles, max_pairs));
+#endif
         if (fused_quant) {
             return f16 ? launch_gemm_pair_inst<__half, true>((int)max_pairs, tiles, st, pa, pb, p)
                        : launch_gemm_pair_inst<__nv_bfloat16, true>((int)max_pairs, tiles, st, pa, pb, p);
@@ -497,11 +509,7 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     CUtensorMap ta, tb;
     int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM);
     if (rcode != 0) return rcode;
-    if (b_mn) {
-        rcode = encode_map_2d(&tb, b, p.N, p.K, 128, kGemmBlockK);
-    } else {
-        rcode = encode_map_2d(&tb, b, p.K, p.N, kGemmBlockK, bn);
-    }
+    rcode = encode_map_2d(&tb, b, p.N, p.K, 128, kGemmBlockK);
     if (rcode != 0) return rcode;
     const uint32_t tiles = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + bn - 1) / bn);
     int grid = (int)(tiles < (uint32_t)rc.num_sms ? tiles : (uint32_t)rc.num_sms);
@@ -512,39 +520,22 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         p.splitk_flags = rc.splitk_flags;
         p.splitk_epoch = ++rc.splitk_epoch;
     }
-#define CATCCOS_GEMM_CASE(BN, MN)                                                                     \
-    if (bn == BN && b_mn == MN) {                                                                     \
+#ifdef CATCCOS_TRACE
+    rc.trace_grid = grid;
+#endif
+#define CATCCOS_GEMM_CASE(BN)                                                                         \
+    if (bn == BN) {                                                                                   \
         if (fused_quant) {                                                                            \
-            return f16 ? launch_gemm_inst<BN, MN, __half, true>(grid, st, ta, tb, p, overlap_predecessor)        \
-                       : launch_gemm_inst<BN, MN, __nv_bfloat16, true>(grid, st, ta, tb, p, overlap_predecessor); \
+            return f16 ? launch_gemm_inst<BN, __half, true>(grid, st, ta, tb, p, overlap_predecessor)         \
+                       : launch_gemm_inst<BN, __nv_bfloat16, true>(grid, st, ta, tb, p, overlap_predecessor); \
         }                                                                                             \
-        return f16 ? launch_gemm_inst<BN, MN, __half, false>(grid, st, ta, tb, p, overlap_predecessor)        \
-                   : launch_gemm_inst<BN, MN, __nv_bfloat16, false>(grid, st, ta, tb, p, overlap_predecessor); \
+        return f16 ? launch_gemm_inst<BN, __half, false>(grid, st, ta, tb, p, overlap_predecessor)           \
+                   : launch_gemm_inst<BN, __nv_bfloat16, false>(grid, st, ta, tb, p, overlap_predecessor);   \
     }
-    CATCCOS_GEMM_CASE(256, true)
-    CATCCOS_GEMM_CASE(256, false)
-    CATCCOS_GEMM_CASE(128, true)
-    CATCCOS_GEMM_CASE(128, false)
+    CATCCOS_GEMM_CASE(256)
+    CATCCOS_GEMM_CASE(128)
 #undef CATCCOS_GEMM_CASE
     return CATCCOS_B200_EINVAL;
-}
-
-__global__ void transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
-                                    uint32_t cols)
-{
-    __shared__ uint8_t tile[64][65];
-    const uint32_t c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
-    for (uint32_t i = threadIdx.y; i < 64; i += blockDim.y) {
-        uint32_t r = r0 + i, c = c0 + threadIdx.x;
-        tile[i][threadIdx.x] = (r < rows && c < cols) ? in[(size_t)r * cols + c] : 0;
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.y; i < 64; i += blockDim.y) {
-        uint32_t c = c0 + i, r = r0 + threadIdx.x;
-        if (c < cols && r < rows) {
-            out[(size_t)c * rows + r] = tile[threadIdx.x][i];
-        }
-    }
 }
 
 // Common part of the two AllGather-Matmul entry points.
@@ -602,7 +593,7 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         // that the first wave's rows are whole early.  A single-wave GEMM starts every tile at once and is
         // better served by one group (segment-major over all rows).
         const uint32_t tiles = ((W * M + 127) / 128) * ((N + 255) / 256);
-        q.group_chunks = tiles > (uint32_t)rc.num_sms ? (g.group_rows > 0 ? (uint32_t)g.group_rows / kRowsPerChunk : 16u) : 0u;
+        q.group_chunks = tiles > (uint32_t)rc.num_sms ? 256u / kRowsPerChunk : 0u;
     }
     {
         // a split-K GEMM on this rank wants the first K segment of each of its K parts first, then the second
@@ -667,17 +658,15 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         p.flags = nullptr;  // stream order is the only dependency
         return launch_gemm(rc, st, a_stage, b, p, false, true);
     }
-    if (produce && consume && (fuse_mode == 0 || fuse_mode == 4)) {
-        // one launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
-        // warps of all ranks consume behind them
+    if (produce) {
+        // one GEMM launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
+        // warps of all ranks consume behind them.  The producer half alone (the harness that hosts several ranks
+        // on one GPU runs every rank's producer before any consumer) is the same launch with the GEMM warps idle.
+        p.gemm_off = consume ? 0u : 1u;
         p.q = q;
         p.q.produce = 1;
         p.q.mode = quant_mode(prequant);
         p.q.e5m2 = g.a_dtype == 1 ? 1u : 0u;
-        if (g.push_mode == 1) {
-            p.q.sys_scope = quant_sys_scope(W);
-            return launch_gemm(rc, st, a_stage, b, p, true);
-        }
         p.q.sys_scope = 0;
         const bool quant_first = fuse_mode == 4;
         PushParams& ps = p.push;
@@ -704,6 +693,7 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         ps.group_chunks = q.group_chunks;
         ps.seg_order_n = q.seg_order_n;
         memcpy(ps.seg_order, q.seg_order, sizeof(ps.seg_order));
+        ps.max_workers = (uint32_t)g.push_workers;
         ps.timeout_ns = g.timeout_ns;
         ps.status = rc.status;
         if (quant_first) {
@@ -717,38 +707,8 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         }
         return launch_gemm(rc, st, a_stage, b, p, true, quant_first);
     }
-    if (produce && consume && fuse_mode == 2) {
-        // two launches, GEMM first: its CTAs take the SMs (one each, with the large shared-memory carve-out)
-        // and wait on flags; the producer's CTAs need no shared memory and are scheduled beside them
-        CUDA_TRY(cudaEventRecord(rc.fork, st));
-        CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
-        rcode = launch_gemm(rc, st, a_stage, b, p);
-        if (rcode != 0) return rcode;
-        rcode = launch_quant_push(rc, rc.side, q, prequant, true);
-        if (rcode != 0) return rcode;
-        CUDA_TRY(cudaEventRecord(rc.join, rc.side));
-        CUDA_TRY(cudaStreamWaitEvent(st, rc.join, 0));
-        return 0;
-    }
-    if (produce) {
-        // two launches: the producer on the side stream, the GEMM on the caller's stream beside it
-        cudaStream_t qs = consume ? rc.side : st;
-        if (consume) {
-            CUDA_TRY(cudaEventRecord(rc.fork, st));
-            CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.fork, 0));
-        }
-        rcode = launch_quant_push(rc, qs, q, prequant, true);
-        if (rcode != 0) return rcode;
-        if (consume) {
-            CUDA_TRY(cudaEventRecord(rc.join, rc.side));
-        }
-    }
-    if (consume) {
-        rcode = launch_gemm(rc, st, a_stage, b, p);
-        if (rcode != 0) return rcode;
-        if (produce) {
-            CUDA_TRY(cudaStreamWaitEvent(st, rc.join, 0));
-        }
+    if (consume) {  // the consumer half alone: the flag-gated GEMM
+        return launch_gemm(rc, st, a_stage, b, p);
     }
     return 0;
 }
@@ -1181,20 +1141,6 @@ int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const
     return launch_gemm(rc, (cudaStream_t)stream, a, b, p);
 }
 
-int catccos_b200_transpose_weight(void* stream, const void* b, void* bt, uint32_t k, uint32_t n)
-{
-    if (!b || !bt || k == 0 || n == 0) {
-        return CATCCOS_B200_EINVAL;
-    }
-    int rcode = ensure_init();
-    if (rcode != 0) return rcode;
-    dim3 grid((n + 63) / 64, (k + 63) / 64), block(64, 4);
-    transpose_u8_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const uint8_t*)b, (uint8_t*)bt, k, n);
-    g_launches++;
-    CUDA_TRY(cudaGetLastError());
-    return 0;
-}
-
 int catccos_b200_last_status(uint32_t out[4])
 {
     if (out == nullptr || g.mode == Mode::kNone) {
@@ -1226,32 +1172,24 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.tiny_block_rule = (int)value;
     } else if (k == "c_dtype" && (value == 0 || value == 1)) {
         g.c_dtype = (int)value;
-    } else if (k == "b_layout" && (value == 0 || value == 1)) {
-        g.b_layout = (int)value;
-    } else if (k == "block_n" && (value == 0 || value == 128 || value == 256)) {
-        g.block_n = (int)value;
-    } else if (k == "timeout_ms" && value > 0 && value <= 600000) {
-        g.timeout_ns = (uint64_t)value * 1000000ull;
-    } else if (k == "phase_mask" && value >= 1 && value <= 3) {
-        g.phase_mask = (int)value;
-    } else if (k == "publish_scope" && value >= 0 && value <= 2) {
-        g.publish_scope = (int)value;
-    } else if (k == "cta_pair" && value >= 0 && value <= 2) {
-        g.cta_pair = (int)value;
-    } else if (k == "group_rows" && value >= 0 && value <= 65536 && value % 16 == 0) {
-        g.group_rows = (int)value;
-    } else if (k == "push_mode" && (value == 0 || value == 1)) {
-        g.push_mode = (int)value;
-    } else if (k == "fuse_mode" && value >= -1 && value <= 4) {
-        g.fuse_mode = (int)value;
     } else if (k == "a_dtype" && (value == 0 || value == 1)) {
         g.a_dtype = (int)value;
     } else if (k == "b_dtype" && (value == 0 || value == 1)) {
         g.b_dtype = (int)value;
-    } else if (k == "split_k" && value >= 0 && value <= 8) {
+    } else if (k == "timeout_ms" && value > 0 && value <= 600000) {
+        g.timeout_ns = (uint64_t)value * 1000000ull;
+    } else if (k == CATCCOS_B200_OPT_BLOCK_N && (value == 0 || value == 128 || value == 256)) {
+        g.block_n = (int)value;
+    } else if (k == CATCCOS_B200_OPT_PHASE_MASK && value >= 1 && value <= 3) {
+        g.phase_mask = (int)value;
+    } else if (k == CATCCOS_B200_OPT_CTA_PAIR && value >= 0 && value <= 2) {
+        g.cta_pair = (int)value;
+    } else if (k == CATCCOS_B200_OPT_FUSE_MODE && (value == -1 || value == 0 || value == 3 || value == 4)) {
+        g.fuse_mode = (int)value;
+    } else if (k == CATCCOS_B200_OPT_SPLIT_K && value >= 0 && value <= 8) {
         g.split_k = (int)value;
-    } else if (k == "quant_items_per_sm" && value >= 1 && value <= 16) {
-        g.quant_items_per_sm = (int)value;
+    } else if (k == CATCCOS_B200_OPT_PUSH_WORKERS && value >= 0 && value <= 65536) {
+        g.push_workers = (int)value;
     } else {
         ERROR_LOG("set_option: unknown key or bad value: %s = %lld", key, (long long)value);
         return CATCCOS_B200_EINVAL;
@@ -1381,3 +1319,35 @@ extern "C" int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_b
     q.timeout_ns = g.timeout_ns;
     return launch_gemm(rc, st, sd.ptr + kStaticCodesOff, b, p, true);
 }
+
+#ifdef CATCCOS_TRACE
+// =============================================================================================
+// Device-side timeline (trace build only; declarations: include/catccos_b200_trace.h)
+// =============================================================================================
+extern "C" int catccos_b200_trace_arm(void)
+{
+    if (g.mode == Mode::kNone) {
+        return CATCCOS_B200_ESTATE;
+    }
+    g.trace_armed = true;
+    return 0;
+}
+
+extern "C" int catccos_b200_trace_read(unsigned long long* out, uint32_t max_words, uint32_t* grid, uint32_t* slots)
+{
+    if (out == nullptr || grid == nullptr || slots == nullptr || g.mode == Mode::kNone) {
+        return CATCCOS_B200_ESTATE;
+    }
+    RankCtx& rc = cur();
+    const size_t words = (size_t)rc.trace_grid * kTraceSlots;
+    if (rc.trace == nullptr || words == 0 || words > max_words) {
+        return CATCCOS_B200_EINVAL;
+    }
+    CUDA_TRY(cudaSetDevice(rc.device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpy(out, rc.trace, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    *grid = (uint32_t)rc.trace_grid;
+    *slots = kTraceSlots;
+    return 0;
+}
+#endif

@@ -1,7 +1,9 @@
 // Shared device helpers for the sm_100a kernels: status words, bounded waits, mbarrier / TMA /
-// tcgen05 PTX wrappers.  Every spin in this library goes through a bounded wait: when the limit
-// runs out the waiter records what it was waiting for in the status block and carries on, so a
-// kernel always runs to its end (and frees its tensor memory) even when a peer never shows up.
+// tcgen05 PTX wrappers.  Every spin in this library goes through a bounded wait.  When a limit runs
+// out the waiter records what it was waiting for in the status block; from then on the status word
+// is non-zero and every other wait of the kernel gives up as soon as it looks (a few hundred polls),
+// so that the kernel drains within microseconds instead of one limit per wait, frees its tensor
+// memory and returns even when a peer never shows up.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -85,7 +87,14 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v)
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t want, uint64_t timeout_ns)
+// True once some waiter of this kernel (or of an earlier, unread one) has given up.
+__device__ __forceinline__ bool status_tripped(const StatusBlock* st)
+{
+    return st != nullptr && *reinterpret_cast<const volatile uint32_t*>(&st->code) != 0u;
+}
+
+__device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t want, uint64_t timeout_ns,
+                                                 const StatusBlock* st = nullptr)
 {
     if ((int32_t)(ld_acquire_gpu(flag) - want) >= 0) {
         return true;
@@ -97,7 +106,7 @@ __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t 
             return true;
         }
         if ((++spins & 0x3Fu) == 0u) {
-            if (globaltimer_ns() - t0 > timeout_ns) {
+            if (globaltimer_ns() - t0 > timeout_ns || status_tripped(st)) {
                 return false;
             }
             __nanosleep(32);
@@ -105,25 +114,25 @@ __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t 
     }
 }
 
-// Waits until *flag >= want (epochs only grow).  Returns false when timeout_ns ran out.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t timeout_ns)
+// Waits until *flag >= want (epochs only grow).  Returns false when timeout_ns ran out or another waiter
+// has already given up.  The spin reads with relaxed system-scope loads (every poll is one L2 access and
+// nothing else); the acquire that orders the data behind the flag is done once, when the value is there.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t timeout_ns,
+                                             const StatusBlock* st = nullptr)
 {
-    if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) {
-        return true;
-    }
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (true) {
-        if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) {
-            return true;
-        }
-        if ((++spins & 0x3Fu) == 0u) {
-            if (globaltimer_ns() - t0 > timeout_ns) {
-                return false;
+    if ((int32_t)(ld_relaxed_sys(flag) - want) < 0) {
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while ((int32_t)(ld_relaxed_sys(flag) - want) < 0) {
+            if ((++spins & 0x3Fu) == 0u) {
+                if (globaltimer_ns() - t0 > timeout_ns || status_tripped(st)) {
+                    return false;
+                }
+                __nanosleep(64);
             }
-            __nanosleep(64);
         }
     }
+    return (int32_t)(ld_acquire_sys(flag) - want) >= 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -169,10 +178,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded mbarrier wait.  The limit (about two seconds of polling) is far beyond any legitimate
-// wait inside one kernel; if it runs out the kernel records a status and continues with whatever
-// is in shared memory, which keeps the grid from hanging on a protocol bug.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id, uint32_t stage)
+// Bounded mbarrier wait.  limit_ns is set by the host above the peer-flag limit (a barrier may legitimately
+// wait for as long as the flag wait it depends on); if it runs out, or another waiter has already given up,
+// the caller gets false and carries on with whatever is in shared memory, which keeps the grid from hanging.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id, uint32_t stage,
+                                          uint64_t limit_ns)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
@@ -180,12 +190,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Status
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFFu) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
-            report_status(st, kStatusBarrierTimeout, id, stage, parity);
-            return false;
+        if ((++spins & 0xFFu) == 0u) {
+            if (status_tripped(st)) {
+                return false;
+            }
+            if (globaltimer_ns() - t0 > limit_ns) {
+                report_status(st, kStatusBarrierTimeout, id, stage, parity);
+                return false;
+            }
         }
     }
     return true;
+}
+
+// The same wait made by all 32 lanes of a warp, with one answer for the warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id,
+                                               uint32_t stage, uint64_t limit_ns)
+{
+    return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, st, id, stage, limit_ns));
 }
 
 __device__ __forceinline__ void fence_proxy_async_shared()
@@ -441,39 +463,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_a
                  : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait on a barrier that the other CTA of the pair arrives on.  What these barriers guard moves
 // through the async proxies (TMA, tcgen05), so the default CTA-scope acquire is what is needed; a
 // cluster-scope acquire on every poll costs several hundred nanoseconds.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, StatusBlock* st, uint32_t id,
-                                                  uint32_t stage)
+                                                  uint32_t stage, uint64_t limit_ns)
 {
-    if (mbar_try_wait_cluster(bar, parity)) {
-        return true;
-    }
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++spins & 0xFFu) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
-            report_status(st, kStatusBarrierTimeout, id, stage, parity);
-            return false;
-        }
-    }
-    return true;
+    return mbar_wait(bar, parity, st, id, stage, limit_ns);
 }
 
 // TMA tile load issued by either CTA of a pair; the completion bytes are credited to the barrier at

@@ -1,0 +1,22 @@
+// Keys of catccos_b200_set_option that are test and tuning hooks, not part of the public boundary
+// (include/catccos_b200.h lists the keys a caller may rely on).  The GPU tests use them to force every
+// kernel variant through the same C ABI the operators use; a caller never needs them.
+#pragma once
+
+// 0 = automatic, 128 or 256: width of the single-CTA GEMM tile
+#define CATCCOS_B200_OPT_BLOCK_N "block_n"
+// bit 0 = launch the producer half, bit 1 = launch the consumer half (default 3).  The harness that hosts
+// several ranks on ONE GPU runs every rank's producer before any consumer, because kernels of different
+// ranks must not wait on one another while they share a device.
+#define CATCCOS_B200_OPT_PHASE_MASK "phase_mask"
+// 0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2), 2 = never
+#define CATCCOS_B200_OPT_CTA_PAIR "cta_pair"
+// -1 = automatic (0 with several ranks, 3 with one); 0 = quantise and pusher warps inside the GEMM kernel (one
+// launch); 3 = one rank only: quantise kernel, then GEMM kernel on the same stream; 4 = quantise kernel into the
+// local stage, then the GEMM kernel whose pusher warps forward the stage to the peers
+#define CATCCOS_B200_OPT_FUSE_MODE "fuse_mode"
+// 0 = automatic (K is cut in up to eight parts when the output tiles would leave half of the SMs idle),
+// 1 = never, 2..8 = at most that many parts
+#define CATCCOS_B200_OPT_SPLIT_K "split_k"
+// 0 = every pusher warp of the grid forwards work items to the peers, else only the first N of them
+#define CATCCOS_B200_OPT_PUSH_WORKERS "push_workers"

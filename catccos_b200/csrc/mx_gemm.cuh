@@ -7,8 +7,7 @@
 //
 //   A      E4M3 codes, row-major [Mg, K]   (K-major operand; Mg = world * M_local gathered rows)
 //   SFA    E8M0 bytes, row-major [Mg, K/32]
-//   B      E4M3 codes, row-major [K, N]    (MN-major operand, read in place)   -- or --
-//          the transposed copy [N, K]      (K-major operand, made once by the weight-prepare kernel)
+//   B      E4M3 codes, row-major [K, N]    (MN-major operand, read in place)
 //   SFB    E8M0 bytes in the reference's file layout [K/64, N, 2]
 //   C      bf16 or fp16, row-major [Mg, N]
 //
@@ -29,9 +28,12 @@
 // (and of the peers' launches) consume behind them, so the quantisation, the allgather and the matmul are one
 // kernel.
 //
-// When `flags` is set, a tile is not touched before every (source rank, 16-row chunk) under its
-// rows has been published with the current epoch by the quantise-and-push kernel; tiles are
-// visited in the order the chunks arrive (own shard first, then chunk by chunk over the peers).
+// When `flags` is set, a K segment of a tile is not touched before every (source rank, 16-row chunk) under
+// the tile's rows has published that segment with the current epoch; tiles are visited in the order the
+// chunks arrive (own shard first, then slice by slice over the peers).  Only the TMA producer polls the
+// flags as a rule (one lane per chunk, relaxed loads, one acquire at the end) and tells the scale loaders
+// through a word in shared memory how far the data is known to be there; a scale loader that is ahead of the
+// producer polls for itself.
 #pragma once
 
 #include <cuda.h>
@@ -64,8 +66,11 @@ struct GemmParams {
     uint32_t flag_stride;
     uint32_t segs, seg_ktiles;
     uint32_t world, rank, m_local, epoch;
-    uint64_t timeout_ns;
+    uint32_t gemm_off;        // 1: the GEMM warps stay idle (the producer half of a call, run apart)
+    uint64_t timeout_ns;      // limit of a wait for ready flags
+    uint64_t bar_timeout_ns;  // limit of a wait on an intra-kernel barrier (set above timeout_ns by the host)
     StatusBlock* status;
+    unsigned long long* trace;  // timeline side buffer (trace build only), else nullptr
     QuantPushParams q;  // the producer's work when the quantise warps ride in this kernel (local stage only)
     PushParams push;    // the pusher warps' work: local stage -> the peers' stages
     // Split K (ksplit > 1): K is cut in ksplit equal parts and every (tile, part) pair is a work unit of its
@@ -95,6 +100,7 @@ struct GemmSmem {
     // overlap_free[2]
     static constexpr uint32_t kNumBars = 2 * kStages + 6 + 4;  // + one per epilogue warp for the split-K reduction
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr uint32_t kOffGate = kOffTmemPtr + 8;  // K-tile iterations whose rows the producer has seen ready
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack to align the base to 1024 bytes
     // Tensor memory: two 128 x BLOCK_N fp32 accumulators and one set of scale factors per stage (12 columns:
@@ -143,26 +149,53 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, 
 }
 
 // Waits (whole warp) until K segment `seg` of every chunk under gathered rows [m0, m0 + 128) carries the epoch.
-__device__ __forceinline__ void wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane, uint32_t seg)
+// A lane looks at four rows and polls a flag only for a row that is the first of its (source, chunk) inside
+// the tile, so every flag is polled by exactly one lane.  Returns false (on every lane) when a wait ran out.
+__device__ __forceinline__ bool wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane, uint32_t seg)
 {
-    uint32_t prev_src = 0xFFFFFFFFu, prev_chunk = 0xFFFFFFFFu;
+    bool ok = true;
     for (uint32_t i = 0; i < 4; ++i) {
-        uint32_t row = m0 + lane * 4 + i;
+        const uint32_t row = m0 + lane * 4 + i;
         if (row >= p.Mg) {
             break;
         }
-        uint32_t src = row / p.m_local;
-        uint32_t chunk = (row - src * p.m_local) / kRowsPerChunk;
-        if (src == prev_src && chunk == prev_chunk) {
+        const uint32_t src = row / p.m_local;
+        const uint32_t in_src = row - src * p.m_local;
+        // first row of the tile, of a source's shard, or of a 16-row chunk
+        if (row != m0 && in_src != 0u && (in_src % kRowsPerChunk) != 0u) {
             continue;
         }
-        prev_src = src;
-        prev_chunk = chunk;
-        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk * p.segs + seg, p.epoch, p.timeout_ns)) {
+        const uint32_t chunk = in_src / kRowsPerChunk;
+        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk * p.segs + seg, p.epoch, p.timeout_ns, p.status)) {
             report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
+            ok = false;
         }
     }
-    __syncwarp();
+    return __all_sync(0xFFFFFFFFu, ok);
+}
+
+__device__ __forceinline__ void st_release_cta_shared(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+
+// After an aborted pipeline (a wait ran out) operand loads and MMAs may still be in flight: the warp that
+// frees the tensor memory, and with it the last warp of the CTA to leave, gives them time to land.
+__device__ __forceinline__ void drain_after_abort(const StatusBlock* st)
+{
+    if (status_tripped(st)) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 50000ull) {
+            __nanosleep(1000);
+        }
+    }
 }
 
 template <typename OutT>
@@ -209,7 +242,7 @@ __device__ __forceinline__ void store_c_chunk(OutT* c, const GemmParams& p, uint
     }
 }
 
-template <uint32_t BLOCK_N, bool B_MN_MAJOR, typename OutT, bool FUSED_QUANT>
+template <uint32_t BLOCK_N, typename OutT, bool FUSED_QUANT>
 __global__ void __launch_bounds__(FUSED_QUANT ? kGemmFusedThreads : kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
 {
@@ -227,16 +260,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* overlap_free = tmem_empty + 2;
     uint64_t* red_bar = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
+    uint32_t* gate = reinterpret_cast<uint32_t*>(smem + S::kOffGate);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
 
     const uint32_t m_tiles = (p.Mg + kGemmBlockM - 1) / kGemmBlockM;
     const uint32_t n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
-    const uint32_t num_tiles = m_tiles * n_tiles;
+    const uint32_t num_tiles = p.gemm_off ? 0u : m_tiles * n_tiles;
     const uint32_t k_tiles = p.K / kGemmBlockK;
+    const uint64_t bar_ns = p.bar_timeout_ns;
 
     if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrCtaStart);
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 2);  // the producer's expect_tx arrival and one scale-loader warp
             mbar_init(&empty[s], 1);
@@ -249,6 +285,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (uint32_t w = 0; w < 4; ++w) {
             mbar_init(&red_bar[w], 1);
         }
+        *gate = 0u;
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -261,6 +298,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrSetupDone);
+    }
 
     if (warp == 4) {
         // ------------------------------- TMA producer -------------------------------------
@@ -268,38 +308,49 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
         const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
         const uint32_t num_units = num_tiles * ksplit;
-        uint32_t it = 0;
-        for (uint32_t unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+        uint32_t it = 0, ti = 0;
+        bool alive = true;
+        for (uint32_t unit = blockIdx.x; alive && unit < num_units; unit += gridDim.x, ++ti) {
             const uint32_t ks = unit / num_tiles;
             TileCoord tc = tile_coord(unit - ks * num_tiles, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
             const uint32_t kt0 = ks * kper;
-            for (uint32_t kt = kt0; kt < kt0 + kper; ++kt, ++it) {
+            for (uint32_t kt = kt0; alive && kt < kt0 + kper; ++kt, ++it) {
                 if (p.flags != nullptr && (kt == kt0 || kt % p.seg_ktiles == 0)) {
-                    wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    const unsigned long long t0 = CATCCOS_TR_NOW();
+                    (void)t0;
+                    alive = wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
                     fence_proxy_async_all();
+                    if (lane == 0) {
+                        // the scale loaders may go ahead up to the end of this K segment (or of the unit)
+                        const uint32_t seg_end = min((kt / p.seg_ktiles + 1u) * p.seg_ktiles, kt0 + kper);
+                        st_release_cta_shared(gate, it + (seg_end - kt));
+                        CATCCOS_TR_ADD(p.trace, kTrProdFlagWaitNs, CATCCOS_TR_NOW() - t0);
+                    }
                 }
-                if (lane == 0) {
+                if (lane == 0 && alive) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    mbar_wait(&empty[s], ph ^ 1u, p.status, 100, s);
+                    const unsigned long long t1 = CATCCOS_TR_NOW();
+                    (void)t1;
+                    alive = mbar_wait(&empty[s], ph ^ 1u, p.status, 100, s, bar_ns);
+                    CATCCOS_TR_ADD(p.trace, kTrProdEmptyWaitNs, CATCCOS_TR_NOW() - t1);
+                    if (kt == kt0 && ti < kTraceTiles) {
+                        CATCCOS_TR_STAMP(p.trace, kTrTileStart + ti);
+                    }
+                    CATCCOS_TR_STAMP_FIRST(p.trace, kTrProdFirstTma);
                     mbar_arrive_expect_tx(&full[s], S::kABytes + S::kBBytes);
                     tma_load_2d(smem + S::kOffA + s * S::kABytes, &tmap_a, &full[s], (int32_t)(kt * kGemmBlockK),
                                 (int32_t)m0);
-                    if constexpr (B_MN_MAJOR) {
-                        // [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
-                        for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
-                            tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full[s],
-                                        (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
-                        }
-                    } else {
-                        // transposed copy [N, K]: box = 128 (K, contiguous) x BLOCK_N rows
-                        tma_load_2d(smem + S::kOffB + s * S::kBBytes, &tmap_b, &full[s],
-                                    (int32_t)(kt * kGemmBlockK), (int32_t)n0);
+                    // B is [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
+                    for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
+                        tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full[s],
+                                    (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
                     }
+                    CATCCOS_TR_STAMP(p.trace, kTrProdLastTma);
                 }
-                __syncwarp();
+                alive = __all_sync(0xFFFFFFFFu, alive);
             }
         }
     } else if (warp == 5) {
@@ -308,7 +359,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // else can (the MMAs, and the commit that releases the stage) and nothing more: four MMAs of 128 cycles
         // each leave it enough time for the commit, the wait for the next stage and its address arithmetic.
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, B_MN_MAJOR) | (p.a_e5m2 ? (1u << 7) : 0u) |
+            const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, true) | (p.a_e5m2 ? (1u << 7) : 0u) |
                                    (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
             const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
             const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
@@ -317,28 +368,27 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t total_it = my_units * kper;
 
             // descriptor halves: the high words are constants, the low words are start addresses >> 4
-            const uint32_t hi_ab = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
-            const uint32_t hi_b_mn = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
-            const uint32_t lo_ab_lbo = (uint32_t)make_smem_desc(0, 16, 1024, 2);         // LBO field of A / K-major B
-            const uint32_t lo_b_mn_lbo = (uint32_t)make_smem_desc(0, 16384, 1024, 2);    // LBO field of MN-major B
-            const uint32_t a_lo0 = lo_ab_lbo | (smem_u32(smem + S::kOffA) >> 4);
-            const uint32_t b_lo0 = (B_MN_MAJOR ? lo_b_mn_lbo : lo_ab_lbo) | (smem_u32(smem + S::kOffB) >> 4);
-            const uint32_t b_hi = B_MN_MAJOR ? hi_b_mn : hi_ab;
-            constexpr uint32_t kKbStepA = 32u >> 4;                                  // 32 bytes along K
-            constexpr uint32_t kKbStepB = (B_MN_MAJOR ? 4096u : 32u) >> 4;          // 32 K rows of 128 bytes, or 32 bytes
-            const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
-
-            // Getting K tile `it` (stage s) ready is split in three small steps that are slotted between the
-            // MMAs of the previous K tile, so that no gap between two MMA issues exceeds one MMA's run time.
-            auto stage_wait = [&](uint32_t s, uint32_t ph) {
-                mbar_wait(&full[s], ph, p.status, 103, s);
-                tcgen05_fence_after();
-            };
             // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; K advances 32 bytes in the row.
             // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart, 8-row K groups
-            // 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO); or K-major like A.
+            // 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO).
+            const uint32_t hi_a = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
+            const uint32_t hi_b = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
+            const uint32_t a_lo0 = (uint32_t)make_smem_desc(0, 16, 1024, 2) | (smem_u32(smem + S::kOffA) >> 4);
+            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
+            constexpr uint32_t kKbStepA = 32u >> 4;    // 32 bytes along K
+            constexpr uint32_t kKbStepB = 4096u >> 4;  // 32 K rows of 128 bytes
+            const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
+            bool alive = true;
+
+            auto stage_wait = [&](uint32_t s, uint32_t ph) {
+                const unsigned long long t0 = CATCCOS_TR_NOW();
+                (void)t0;
+                alive = mbar_wait(&full[s], ph, p.status, 103, s, bar_ns);
+                tcgen05_fence_after();
+                CATCCOS_TR_ADD(p.trace, kTrMmaFullWaitNs, CATCCOS_TR_NOW() - t0);
+            };
             auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
-                umma_mxf8_lohi(d_col, a_lo + kb * kKbStepA, hi_ab, b_lo + kb * kKbStepB, b_hi, idesc_with_sf_id(idesc, kb), sf,
+                umma_mxf8_lohi(d_col, a_lo + kb * kKbStepA, hi_a, b_lo + kb * kKbStepB, hi_b, idesc_with_sf_id(idesc, kb), sf,
                                sf + 4, accumulate);
             };
 
@@ -346,16 +396,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 stage_wait(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
-            for (uint32_t ti = 0; ti < my_units; ++ti) {
+            for (uint32_t ti = 0; alive && ti < my_units; ++ti) {
                 const uint32_t acc = ti & 1u;
                 const uint32_t acc_ph = (ti >> 1) & 1u;
                 const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
-                mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, p.status, 101, acc);
-                if (S::kOverlap && ti > 0) {
-                    mbar_wait(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 102, acc);
+                const unsigned long long t0 = CATCCOS_TR_NOW();
+                (void)t0;
+                alive = mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, p.status, 101, acc, bar_ns);
+                if (S::kOverlap && ti > 0 && alive) {
+                    alive = mbar_wait(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 102, acc, bar_ns);
                 }
+                CATCCOS_TR_ADD(p.trace, kTrMmaAccWaitNs, CATCCOS_TR_NOW() - t0);
                 tcgen05_fence_after();
-                for (uint32_t kt = 0; kt < kper; ++kt, ++it) {
+                CATCCOS_TR_STAMP_FIRST(p.trace, kTrMmaFirst);
+                for (uint32_t kt = 0; alive && kt < kper; ++kt, ++it) {
                     const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
                     const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
                     const uint32_t sf = sf_tmem0 + s * S::kSfSetCols;
@@ -374,6 +428,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     ph = ph_next;
                 }
                 tcgen05_commit(&tmem_full[acc]);
+                if (ti < kTraceTiles) {
+                    CATCCOS_TR_STAMP(p.trace, kTrTileEnd + ti);
+                }
+                CATCCOS_TR_STAMP(p.trace, kTrMmaLast);
             }
         }
         __syncwarp();
@@ -388,9 +446,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
-            // pusher pw of CTA b is worker pw * grid + b: when there are fewer units than pushers (two ranks) the work
-            // spreads over all SMs instead of filling the first CTAs' six pushers
-            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps);
+            // pusher pw of CTA b is worker pw * grid + b: a short item list spreads over all SMs instead of
+            // filling the first CTAs' six pushers
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------
@@ -410,6 +468,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
         uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
         uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+        bool alive = true;
 
         auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
             const uint32_t seq = it / kper;
@@ -422,14 +481,22 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
                 gated_seq = seq;
                 gated_seg = kt / p.seg_ktiles;
-                wait_rows_ready(p, m0, lane, gated_seg);
+                // the producer has usually seen this segment's flags already and said so in shared memory
+                if (ld_acquire_cta_shared(gate) <= it) {
+                    const unsigned long long t0 = CATCCOS_TR_NOW();
+                    (void)t0;
+                    alive = wait_rows_ready(p, m0, lane, gated_seg) && alive;
+                    if (lane == 0) {
+                        CATCCOS_TR_ADD(p.trace, kTrSfGateWaitNs + j, CATCCOS_TR_NOW() - t0);
+                    }
+                }
             }
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
                 const uint32_t row = m0 + i * 32 + lane;
                 ra[i] = 0x7F7F7F7Fu;
                 if (row < p.Mg) {
-                    ra[i] = *reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u);
+                    ra[i] = __ldcg(reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u));
                 }
             }
 #pragma unroll
@@ -448,14 +515,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (it < total_it) {
             issue_loads(it, cur_a, cur_lo, cur_hi);
         }
-        for (; it < total_it; it += kSfWarps) {
+        for (; alive && it < total_it; it += kSfWarps) {
             const bool has_next = it + kSfWarps < total_it;
             if (has_next) {
                 issue_loads(it + kSfWarps, nxt_a, nxt_lo, nxt_hi);
             }
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            mbar_wait(&empty[s], ph ^ 1u, p.status, 105, s);
+            const unsigned long long t1 = CATCCOS_TR_NOW();
+            (void)t1;
+            alive = mbar_wait_warp(&empty[s], ph ^ 1u, p.status, 105, s, bar_ns) && alive;
+            if (lane == 0) {
+                CATCCOS_TR_ADD(p.trace, kTrSfEmptyWaitNs + j, CATCCOS_TR_NOW() - t1);
+            }
             uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
             uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
             *reinterpret_cast<uint4*>(sfa + lane * 16u) = make_uint4(cur_a[0], cur_a[1], cur_a[2], cur_a[3]);
@@ -503,7 +575,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         constexpr uint32_t kChunks = BLOCK_N / 32;
         const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
         const uint32_t num_units = num_tiles * ksplit;
-        if (ksplit > 1u) {
+        if (ksplit > 1u && num_tiles > 0u) {
             // Split K: this CTA is work unit blockIdx.x = (tile, part ks) and the only one on its SM.  Each part
             // owns kChunks / ksplit of the tile's 32-column chunks.  A part first writes the chunks it does not
             // own to its partial tile in the workspace ([part][chunk][128 rows x 32 floats], 4 KiB per chunk and
@@ -523,7 +595,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             constexpr uint32_t kPieceBytes = 32u * 32u * 4u;  // 32 rows x 32 floats
             float* parts = p.splitk_ws + (size_t)tile * ksplit * kPartFloats;
             uint32_t* flags = p.splitk_flags + (size_t)tile * ksplit * 4u;
-            mbar_wait(&tmem_full[0], 0, p.status, 106, 0);
+            bool alive = mbar_wait_warp(&tmem_full[0], 0, p.status, 106, 0, bar_ns);
             tcgen05_fence_after();
             // a warp whose 32 rows all lie below the matrix has nothing to add up (its peers in the other
             // parts take the same decision, so nobody waits for its flag); lanes below the matrix skip
@@ -556,11 +628,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     st_release_gpu(flags + ks * 4u + q, p.splitk_epoch);
                 }
                 // lanes 0 .. ksplit-1 each watch one part's flag (the polls overlap instead of queueing up)
-                if (lane < ksplit && lane != ks && !wait_flag_ge_gpu(flags + lane * 4u + q, p.splitk_epoch, p.timeout_ns)) {
+                bool ok = true;
+                if (lane < ksplit && lane != ks &&
+                    !wait_flag_ge_gpu(flags + lane * 4u + q, p.splitk_epoch, p.timeout_ns, p.status)) {
                     report_status(p.status, kStatusFlagTimeout, 0x100u + lane, tile, p.splitk_epoch);
+                    ok = false;
                 }
-                __syncwarp();
-                if (lane == 0) {
+                alive = __all_sync(0xFFFFFFFFu, ok) && alive;
+                if (lane == 0 && alive) {
                     mbar_arrive_expect_tx(&red_bar[q], (ksplit - 1u) * cps * kPieceBytes);
                     fence_proxy_async_all();  // the other parts' generic-proxy stores before this thread's bulk copies
                     uint32_t slot = 0;
@@ -576,8 +651,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                 }
                 __syncwarp();
-                mbar_wait(&red_bar[q], 0, p.status, 107, q);
-                for (uint32_t oc = 0; oc < cps; ++oc) {
+                alive = mbar_wait_warp(&red_bar[q], 0, p.status, 107, q, bar_ns) && alive;
+                // a part that gave up writes nothing: C keeps what the caller put there
+                for (uint32_t oc = 0; alive && oc < cps; ++oc) {
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (own0 + oc) * 32u, r);
                     tmem_ld_wait();
@@ -606,9 +682,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
             }
             tcgen05_fence_before();
+            if (q == 0 && lane == 0) {
+                CATCCOS_TR_STAMP(p.trace, kTrEpiLast);
+            }
         }
         uint32_t ti = 0;
-        for (uint32_t unit = blockIdx.x; ksplit == 1u && unit < num_units; unit += gridDim.x, ++ti) {
+        bool alive = true;
+        for (uint32_t unit = blockIdx.x; alive && ksplit == 1u && unit < num_units; unit += gridDim.x, ++ti) {
             const uint32_t ks = unit / num_tiles;
             const uint32_t tile = unit - ks * num_tiles;
             TileCoord tc = tile_coord(tile, n_tiles, m_tiles, p);
@@ -617,7 +697,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t acc = ti & 1u;
             const uint32_t acc_ph = (ti >> 1) & 1u;
             const uint32_t d_col = acc ? S::kAccCol1 : 0u;
-            mbar_wait(&tmem_full[acc], acc_ph, p.status, 106, acc);
+            const unsigned long long t0 = CATCCOS_TR_NOW();
+            (void)t0;
+            alive = mbar_wait_warp(&tmem_full[acc], acc_ph, p.status, 106, acc, bar_ns);
+            if (q == 0 && lane == 0) {
+                CATCCOS_TR_ADD(p.trace, kTrEpiWaitNs, CATCCOS_TR_NOW() - t0);
+            }
+            if (!alive) {
+                break;  // an accumulator that never filled is not written out
+            }
             tcgen05_fence_after();
             const uint32_t row = m0 + q * 32 + lane;
             // the chunks that hold the columns shared with the other accumulator go first: the last two of
@@ -643,13 +731,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&tmem_empty[acc]);
+                if (q == 0) {
+                    CATCCOS_TR_STAMP(p.trace, kTrEpiLast);
+                }
             }
         }
     }
 
     tcgen05_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrCtaEnd);
+    }
     if (warp == 5) {
+        drain_after_abort(p.status);
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }

@@ -37,6 +37,7 @@ struct PairSmem {
     // CTAs' scale loaders have put a stage's atoms into shared memory)
     static constexpr uint32_t kNumBars = 3 * kStages + 6;
     static constexpr uint32_t kOffTmemPtr = kOffBar + kNumBars * 8;
+    static constexpr uint32_t kOffGate = kOffTmemPtr + 8;  // K-tile iterations whose rows this CTA's producer has seen ready
     static constexpr uint32_t kBytes = kOffTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;
     static constexpr uint32_t kOverlapChunks = 2;
@@ -88,19 +89,23 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* overlap_free = tmem_empty + 2;
     uint64_t* atoms_written = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
+    uint32_t* gate = reinterpret_cast<uint32_t*>(smem + S::kOffGate);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();  // 0 = leader
+    const uint64_t bar_ns = p.bar_timeout_ns;
     const uint32_t pair = blockIdx.x >> 1;
     const uint32_t num_pairs = gridDim.x >> 1;
 
     const uint32_t m_tiles = (p.Mg + kPairBlockM - 1) / kPairBlockM;
     const uint32_t n_tiles = (p.N + kPairBlockN - 1) / kPairBlockN;
-    const uint32_t num_tiles = m_tiles * n_tiles;
+    const uint32_t num_tiles = p.gemm_off ? 0u : m_tiles * n_tiles;
     const uint32_t k_tiles = p.K / kGemmBlockK;
 
     if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrCtaStart);
+        *gate = 0u;
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 3);  // both CTAs' producers (expect_tx) and the commit behind the scale copies
             mbar_init(&empty[s], 1);
@@ -125,30 +130,49 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
+    if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrSetupDone);
+    }
+
     if (warp == 4) {
         // ------------------------------- TMA producer (both CTAs) -------------------------
-        uint32_t it = 0;
-        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs) {
+        uint32_t it = 0, ti = 0;
+        bool alive = true;
+        for (uint32_t tile = pair; alive && tile < num_tiles; tile += num_pairs, ++ti) {
             TileCoord tc = pair_tile_coord(tile, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
             const uint32_t n0 = tc.n_tile * kPairBlockN + cta * 128u;
-            for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+            for (uint32_t kt = 0; alive && kt < k_tiles; ++kt, ++it) {
                 if (p.flags != nullptr && kt % p.seg_ktiles == 0) {
-                    wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    const unsigned long long t0 = CATCCOS_TR_NOW();
+                    (void)t0;
+                    alive = wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
                     fence_proxy_async_all();
+                    if (lane == 0) {
+                        st_release_cta_shared(gate, it + (min(kt + p.seg_ktiles, k_tiles) - kt));
+                        CATCCOS_TR_ADD(p.trace, kTrProdFlagWaitNs, CATCCOS_TR_NOW() - t0);
+                    }
                 }
-                if (lane == 0) {
+                if (lane == 0 && alive) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    mbar_wait_cluster(&empty[s], ph ^ 1u, p.status, 200, s);
+                    const unsigned long long t1 = CATCCOS_TR_NOW();
+                    (void)t1;
+                    alive = mbar_wait_cluster(&empty[s], ph ^ 1u, p.status, 200, s, bar_ns);
+                    CATCCOS_TR_ADD(p.trace, kTrProdEmptyWaitNs, CATCCOS_TR_NOW() - t1);
+                    if (kt == 0 && ti < kTraceTiles) {
+                        CATCCOS_TR_STAMP(p.trace, kTrTileStart + ti);
+                    }
+                    CATCCOS_TR_STAMP_FIRST(p.trace, kTrProdFirstTma);
                     const uint32_t leader_bar = map_to_cta(smem_u32(&full[s]), 0);
                     mbar_arrive_expect_tx_cluster(leader_bar, S::kABytes + S::kBBytes);
                     tma_load_2d_pair(smem + S::kOffA + s * S::kABytes, &tmap_a, leader_bar, (int32_t)(kt * kGemmBlockK),
                                      (int32_t)m0);
                     tma_load_2d_pair(smem + S::kOffB + s * S::kBBytes, &tmap_b, leader_bar, (int32_t)n0,
                                      (int32_t)(kt * kGemmBlockK));
+                    CATCCOS_TR_STAMP(p.trace, kTrProdLastTma);
                 }
-                __syncwarp();
+                alive = __all_sync(0xFFFFFFFFu, alive);
             }
         }
     } else if (warp == 5) {
@@ -167,9 +191,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
 
+            bool alive = true;
             auto stage_wait = [&](uint32_t s, uint32_t ph) {
-                mbar_wait_cluster(&full[s], ph, p.status, 203, s);
+                const unsigned long long t0 = CATCCOS_TR_NOW();
+                (void)t0;
+                alive = mbar_wait_cluster(&full[s], ph, p.status, 203, s, bar_ns);
                 tcgen05_fence_after();
+                CATCCOS_TR_ADD(p.trace, kTrMmaFullWaitNs, CATCCOS_TR_NOW() - t0);
             };
             auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
                 umma_mxf8_pair_lohi(d_col, a_lo + kb * (32u >> 4), hi_a, b_lo + kb * (4096u >> 4), hi_b,
@@ -180,16 +208,20 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 stage_wait(0, 0);
             }
             uint32_t it = 0, s = 0, ph = 0;
-            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
+            for (uint32_t ti = 0; alive && ti < my_tiles; ++ti) {
                 const uint32_t acc = ti & 1u;
                 const uint32_t acc_ph = (ti >> 1) & 1u;
                 const uint32_t d_col = tmem_base + (acc ? S::kAccCol1 : 0u);
-                mbar_wait_cluster(&tmem_empty[acc], acc_ph ^ 1u, p.status, 201, acc);
-                if (ti > 0) {
-                    mbar_wait_cluster(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 202, acc);
+                const unsigned long long t0 = CATCCOS_TR_NOW();
+                (void)t0;
+                alive = mbar_wait_cluster(&tmem_empty[acc], acc_ph ^ 1u, p.status, 201, acc, bar_ns);
+                if (ti > 0 && alive) {
+                    alive = mbar_wait_cluster(&overlap_free[acc ^ 1u], ((ti - 1) >> 1) & 1u, p.status, 202, acc, bar_ns);
                 }
+                CATCCOS_TR_ADD(p.trace, kTrMmaAccWaitNs, CATCCOS_TR_NOW() - t0);
                 tcgen05_fence_after();
-                for (uint32_t kt = 0; kt < k_tiles; ++kt, ++it) {
+                CATCCOS_TR_STAMP_FIRST(p.trace, kTrMmaFirst);
+                for (uint32_t kt = 0; alive && kt < k_tiles; ++kt, ++it) {
                     const uint32_t a_lo = a_lo0 + s * (S::kABytes >> 4);
                     const uint32_t b_lo = b_lo0 + s * (S::kBBytes >> 4);
                     const uint32_t sf = sf_tmem0 + s * S::kSfSetCols;
@@ -208,6 +240,10 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     ph = ph_next;
                 }
                 tcgen05_commit_pair(&tmem_full[acc], 3);
+                if (ti < kTraceTiles) {
+                    CATCCOS_TR_STAMP(p.trace, kTrTileEnd + ti);
+                }
+                CATCCOS_TR_STAMP(p.trace, kTrMmaLast);
             }
         }
         __syncwarp();
@@ -222,7 +258,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
-            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps);  // spread over all SMs
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw);  // spread over all SMs
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders (both CTAs) ------------------------
@@ -235,6 +271,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
         uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
         uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+        bool alive = true;
 
         auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
             const uint32_t seq = it / k_tiles;
@@ -245,14 +282,22 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
                 gated_seq = seq;
                 gated_seg = kt / p.seg_ktiles;
-                wait_rows_ready(p, m0, lane, gated_seg);
+                // this CTA's producer has usually seen the segment's flags already and said so in shared memory
+                if (ld_acquire_cta_shared(gate) <= it) {
+                    const unsigned long long t0 = CATCCOS_TR_NOW();
+                    (void)t0;
+                    alive = wait_rows_ready(p, m0, lane, gated_seg) && alive;
+                    if (lane == 0) {
+                        CATCCOS_TR_ADD(p.trace, kTrSfGateWaitNs + j, CATCCOS_TR_NOW() - t0);
+                    }
+                }
             }
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
                 const uint32_t row = m0 + i * 32 + lane;
                 ra[i] = 0x7F7F7F7Fu;
                 if (row < p.Mg) {
-                    ra[i] = *reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u);
+                    ra[i] = __ldcg(reinterpret_cast<const uint32_t*>(p.a_scales + (size_t)row * sf_row_bytes + kt * 4u));
                 }
             }
 #pragma unroll
@@ -271,14 +316,19 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (it < total_it) {
             issue_loads(it, cur_a, cur_lo, cur_hi);
         }
-        for (; it < total_it; it += kSfWarps) {
+        for (; alive && it < total_it; it += kSfWarps) {
             const bool has_next = it + kSfWarps < total_it;
             if (has_next) {
                 issue_loads(it + kSfWarps, nxt_a, nxt_lo, nxt_hi);
             }
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            mbar_wait_cluster(&empty[s], ph ^ 1u, p.status, 205, s);
+            const unsigned long long t1 = CATCCOS_TR_NOW();
+            (void)t1;
+            alive = mbar_wait_warp(&empty[s], ph ^ 1u, p.status, 205, s, bar_ns) && alive;
+            if (lane == 0) {
+                CATCCOS_TR_ADD(p.trace, kTrSfEmptyWaitNs + j, CATCCOS_TR_NOW() - t1);
+            }
             uint8_t* sfa = smem + S::kOffSfa + s * S::kSfaBytes;
             uint8_t* sfb = smem + S::kOffSfb + s * S::kSfbBytes;
             *reinterpret_cast<uint4*>(sfa + lane * 16u) = make_uint4(cur_a[0], cur_a[1], cur_a[2], cur_a[3]);
@@ -300,7 +350,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // a thread gets a tcgen05 instruction out only every ~70 cycles.
                 mbar_arrive_cluster(map_to_cta(smem_u32(&atoms_written[s]), 0));
                 if (cta == 0) {
-                    mbar_wait_cluster(&atoms_written[s], ph, p.status, 207, s);
+                    mbar_wait_cluster(&atoms_written[s], ph, p.status, 207, s, bar_ns);
                     tcgen05_fence_after();
                     const uint32_t hi_sf = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
                     const uint32_t sf_t = tmem_base + S::kSfCol + s * S::kSfSetCols;
@@ -333,7 +383,15 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t acc = ti & 1u;
             const uint32_t acc_ph = (ti >> 1) & 1u;
             const uint32_t d_col = acc ? S::kAccCol1 : 0u;
-            mbar_wait_cluster(&tmem_full[acc], acc_ph, p.status, 206, acc);
+            const unsigned long long t0 = CATCCOS_TR_NOW();
+            (void)t0;
+            const bool alive = mbar_wait_warp(&tmem_full[acc], acc_ph, p.status, 206, acc, bar_ns);
+            if (q == 0 && lane == 0) {
+                CATCCOS_TR_ADD(p.trace, kTrEpiWaitNs, CATCCOS_TR_NOW() - t0);
+            }
+            if (!alive) {
+                break;  // an accumulator that never filled is not written out
+            }
             tcgen05_fence_after();
             const uint32_t row = m0 + q * 32 + lane;
             for (uint32_t ci = 0; ci < kChunks; ++ci) {
@@ -378,6 +436,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+                if (q == 0) {
+                    CATCCOS_TR_STAMP(p.trace, kTrEpiLast);
+                }
             }
         }
     }
@@ -385,7 +446,11 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tcgen05_fence_before();
     __syncthreads();
     cluster_sync_all();  // nobody leaves while the other CTA may still arrive on its barriers
+    if (threadIdx.x == 0) {
+        CATCCOS_TR_STAMP(p.trace, kTrCtaEnd);
+    }
     if (warp == 5) {
+        drain_after_abort(p.status);
         tcgen05_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemCols);
     }

@@ -17,6 +17,7 @@
 #include <cuda_fp4.h>
 
 #include "common.cuh"
+#include "trace.cuh"
 
 namespace catccos {
 
@@ -60,6 +61,7 @@ struct QuantPushParams {
     uint32_t flag_stride;
     uint64_t timeout_ns;
     StatusBlock* status;
+    unsigned long long* trace;    // timeline side buffer (trace build only), else nullptr
 };
 
 __device__ __forceinline__ uint32_t absmax_bits8(uint4 v)
@@ -162,6 +164,8 @@ __device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint3
 // One work item = one (16-row chunk, column segment), owned by exactly one group, which publishes it alone.
 __device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t flag_index, uint32_t tid, uint32_t bar_id)
 {
+    const unsigned long long t0 = CATCCOS_TR_NOW();
+    (void)t0;
     quant_group_sync(bar_id);
     if (tid == 0) {
         if (p.sys_scope) {
@@ -177,6 +181,10 @@ __device__ __forceinline__ void publish_item(const QuantPushParams& p, uint32_t 
                              : "memory");
             }
         }
+        CATCCOS_TR_ADD(p.trace, kTrQuantPublishNs, CATCCOS_TR_NOW() - t0);
+        CATCCOS_TR_ADD(p.trace, kTrQuantItems, 1ull);
+        CATCCOS_TR_STAMP_FIRST(p.trace, kTrQuantFirstDone);
+        CATCCOS_TR_STAMP(p.trace, kTrQuantDone);
     }
 }
 
@@ -310,44 +318,67 @@ __device__ __forceinline__ void quant_push_producer(const QuantPushParams& p, ui
 struct PushParams {
     const uint8_t* src_codes;   // this rank's shard in its own stage: codes [M, K]
     const uint8_t* src_scales;  //                                      scales [M, K/32]
-    const uint32_t* src_flags;  // this GPU's flag words for its own shard (published by the quantise warps)
+    const uint32_t* src_flags;  // this GPU's flag words for its own shard (published by the quantise warps), or
+                                // nullptr when the shard was complete before the kernel started
     uint8_t* dst_codes[kMaxRanks];   // the same shard's place in rank d's stage (nullptr for d == rank)
     uint8_t* dst_scales[kMaxRanks];
     uint32_t* dst_flags[kMaxRanks];  // rank d's flag words for this source
     uint32_t M, K, rank, world, epoch;
     uint32_t segs_per_chunk, seg_cols, group_chunks, seg_order_n;
     uint8_t seg_order[32];
+    uint32_t max_workers;       // 0, or: only the first max_workers pusher warps of the grid take part
     uint64_t timeout_ns;
     StatusBlock* status;
+    unsigned long long* trace;  // timeline side buffer (trace build only), else nullptr
 };
 
-// The pusher: one warp copies finished work items of this rank's shard from the local stage to the peers.
-// A unit of work is (work item, destination); pusher `worker` of `num_workers` takes units worker,
-// worker + num_workers, ... in item order, so early K segments leave first.  It waits (bounded) for the
-// quantise warps' local flag, copies 16 rows x one K segment with several 16-byte loads in flight,
-// fences at system scope and sets the destination's flag.  A plain copy loop like this keeps NVLink
-// busy with one or two warps per SM, which the quantise warps (stalled on HBM loads most of the time)
-// cannot do.
-__device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, uint32_t worker, uint32_t num_workers)
+// The pusher: one warp forwards finished work items of this rank's shard from the local stage to the peers.
+// Pusher `worker` of `num_workers` takes items worker, worker + num_workers, ... in item order, so early K
+// segments leave first.  For an item it waits (bounded) for the quantise warps' local flag, then moves the
+// 16 rows x one K segment in passes of 4 KiB: eight 16-byte loads in flight per lane, each value stored to
+// every peer (the local stage is read once, whatever the number of ranks; the peers are visited starting
+// behind this rank so that the ranks of a box do not all store to the same GPU at the same moment).  One
+// system-scope fence per item orders the stores before the peers' flag words.  `pw` names the pusher inside
+// its CTA (timeline only).
+__device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, uint32_t worker, uint32_t num_workers,
+                                            uint32_t pw)
 {
+    (void)pw;
     if (p.world < 2) {
         return;
+    }
+    if (p.max_workers != 0u) {
+        if (worker >= p.max_workers) {
+            return;
+        }
+        num_workers = min(num_workers, p.max_workers);
     }
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t items = chunks * p.segs_per_chunk;
     const uint32_t peers = p.world - 1;
-    const uint32_t units = items * peers;
     const uint32_t sf_cols = p.K / 32;
-    for (uint32_t u = worker; u < units; u += num_workers) {
-        const uint32_t item = u / peers;
-        const uint32_t d = (p.rank + 1 + (u - item * peers)) % p.world;
+    for (uint32_t item = worker; item < items; item += num_workers) {
         uint32_t chunk, seg;
         item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
         const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
-        if (lane == 0 && !wait_flag_ge(p.src_flags + flag_index, p.epoch, p.timeout_ns)) {
-            report_status(p.status, kStatusFlagTimeout, p.rank, chunk, p.epoch);
+        if (p.src_flags != nullptr) {
+            const unsigned long long t0 = CATCCOS_TR_NOW();
+            (void)t0;
+            bool ok = true;
+            if (lane == 0 && !wait_flag_ge(p.src_flags + flag_index, p.epoch, p.timeout_ns, p.status)) {
+                report_status(p.status, kStatusFlagTimeout, p.rank, chunk, p.epoch);
+                ok = false;
+            }
+            if (!__all_sync(0xFFFFFFFFu, ok)) {
+                return;  // the quantise warps of this launch will not deliver: nothing sensible left to push
+            }
+            if (lane == 0) {
+                CATCCOS_TR_ADD(p.trace, kTrPushFlagWaitNs + pw, CATCCOS_TR_NOW() - t0);
+            }
         }
-        __syncwarp();
+        if (lane == 0) {
+            CATCCOS_TR_STAMP_FIRST(p.trace, kTrPushFirst + pw);
+        }
         const uint32_t c_begin = seg * p.seg_cols;
         const uint32_t cols = min(p.K, c_begin + p.seg_cols) - c_begin;
         const uint32_t r_begin = chunk * kQuantRowsPerItem;
@@ -367,10 +398,13 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
                     v[j] = __ldcg(reinterpret_cast<const uint4*>(p.src_codes + off[j]));
                 }
             }
+            for (uint32_t t = 0; t < peers; ++t) {
+                uint8_t* dst = p.dst_codes[(p.rank + 1 + t) % p.world];
 #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j) {
-                if (i + j * 32 < n16) {
-                    *reinterpret_cast<uint4*>(p.dst_codes[d] + off[j]) = v[j];
+                for (uint32_t j = 0; j < 8; ++j) {
+                    if (i + j * 32 < n16) {
+                        *reinterpret_cast<uint4*>(dst + off[j]) = v[j];
+                    }
                 }
             }
         }
@@ -381,19 +415,34 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
             for (uint32_t e = lane; e < rows * w_per_row; e += 32) {
                 const uint32_t r = e / w_per_row;
                 const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (size_t)(e - r * w_per_row) * 4;
-                *reinterpret_cast<uint32_t*>(p.dst_scales[d] + off) = __ldcg(reinterpret_cast<const uint32_t*>(p.src_scales + off));
+                const uint32_t w = __ldcg(reinterpret_cast<const uint32_t*>(p.src_scales + off));
+                for (uint32_t t = 0; t < peers; ++t) {
+                    *reinterpret_cast<uint32_t*>(p.dst_scales[(p.rank + 1 + t) % p.world] + off) = w;
+                }
             }
         } else {
             for (uint32_t e = lane; e < rows * sf_per_row; e += 32) {
                 const uint32_t r = e / sf_per_row;
                 const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (e - r * sf_per_row);
-                p.dst_scales[d][off] = __ldcg(p.src_scales + off);
+                const uint8_t b = __ldcg(p.src_scales + off);
+                for (uint32_t t = 0; t < peers; ++t) {
+                    p.dst_scales[(p.rank + 1 + t) % p.world][off] = b;
+                }
             }
         }
         __syncwarp();
         if (lane == 0) {
+            const unsigned long long t1 = CATCCOS_TR_NOW();
+            (void)t1;
             __threadfence_system();
-            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[d] + flag_index), "r"(p.epoch) : "memory");
+            CATCCOS_TR_ADD(p.trace, kTrPushFenceNs + pw, CATCCOS_TR_NOW() - t1);
+            for (uint32_t t = 0; t < peers; ++t) {
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[(p.rank + 1 + t) % p.world] + flag_index),
+                             "r"(p.epoch)
+                             : "memory");
+            }
+            CATCCOS_TR_ADD(p.trace, kTrPushItems + pw, 1ull);
+            CATCCOS_TR_STAMP(p.trace, kTrPushLast + pw);
         }
     }
 }
@@ -415,7 +464,7 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
         const uint32_t src = (p.rank + 1 + item % (p.world - 1)) % p.world;
         if (threadIdx.x < p.segs_per_chunk) {
             const uint32_t* f = p.flags + (size_t)src * p.flag_stride + chunk * p.segs_per_chunk + threadIdx.x;
-            if (!wait_flag_ge(f, p.epoch, p.timeout_ns)) {
+            if (!wait_flag_ge(f, p.epoch, p.timeout_ns, p.status)) {
                 report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
             }
         }

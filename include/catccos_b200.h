@@ -129,48 +129,26 @@ int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const
 int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_bf16, const void* b, const void* b_scale, void* c,
                                         uint32_t m, uint32_t n, uint32_t k);
 
-/* Transposed copy of a weight, b [k, n] -> bt [n, k], for option "b_layout" = 1.  No reference
- * counterpart: the reference reads B through CATLASS layout tags (mx_allgather_matmul.hpp:148-151). */
-int catccos_b200_transpose_weight(void* stream, const void* b, void* bt, uint32_t k, uint32_t n);
-
 /* ---- status and options ---------------------------------------------------------------------
  * out[0] code (0 ok, 1 ready-flag timeout, 2 internal barrier timeout, 3 handshake timeout),
  * out[1] rank waited for, out[2] chunk, out[3] epoch.  Synchronises the device, clears the record.
  * The reference has no counterpart: its waits are unbounded (mx_quant_allgather.hpp:179-185). */
 int catccos_b200_last_status(uint32_t out[4]);
 
-/* Options (all ranks must set the same values):
+/* Options (all ranks must set the same values; set them while no call is in flight):
  *   "tiny_block_rule" 0 = CPU golden (amax < 1e-12 -> scale 0x7F), 1 = reference device kernel
  *   "c_dtype"         0 = bf16, 1 = fp16 (the reference's output type, main.cpp:28)
  *   "a_dtype"         element type of the A codes, written by the quantiser and read by the GEMM: 0 = E4M3
  *                     (emax 8, +-448), 1 = E5M2 (emax 15, +-57344; MX_QUANT_DTYPE = 1 in the reference,
  *                     comm_block_mx_quant.hpp:75-76,410)
  *   "b_dtype"         element type of the B codes the caller passes: 0 = E4M3, 1 = E5M2
- *   "b_layout"        0 = b is [k, n] as in the reference files, 1 = b is the transposed copy [n, k]
- *   "block_n"         0 = automatic, 128 or 256 = GEMM tile width
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
- *   "phase_mask"      bit 0 = launch the producer side, bit 1 = launch the consumer side (default 3);
- *                     the single-GPU harness runs all ranks' producers before any consumer.
- *   "cta_pair"        0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2),
- *                     2 = never
- *   "group_rows"      0 = automatic; else the rows (multiple of 16) the producer finishes and sends as one group
- *                     when the GEMM runs in several waves (default 256)
- *   "push_mode"       fused kernel only: 0 = the quantise warps fill the local stage and six pusher warps per
- *                     CTA copy finished items to the peers, 1 = the quantise warps store to every rank themselves
- *   "fuse_mode"       -1 = automatic (default): 0 with several ranks, 3 with one;
- *                     0 = the quantise-and-push warps run inside the GEMM kernel (one launch),
- *                     1 = quantise kernel and GEMM kernel as two launches on two streams, the GEMM gated on flags,
- *                     2 = the same two launches with the GEMM launched first,
- *                     3 = one rank only: quantise kernel, then GEMM kernel, on the caller's stream (no flags),
- *                     4 = quantise kernel into the local stage first, then the GEMM kernel whose pusher warps
- *                         forward the stage to the peers (its quantise warps have nothing to do)
- *   "split_k"         0 = automatic: when the output tiles would occupy at most half of the SMs, K is cut in up to
- *                     eight equal parts, each (tile, part) runs on its own SM and the fp32 partial tiles are added
- *                     in part order through a per-rank scratch allocated when the rank is set up; 1 = never;
- *                     2..8 = at most that many parts.  Because of that scratch (and the symmetric buffer's
- *                     epochs) the operator calls of one rank must not overlap on the GPU.
- *   "publish_scope"   0 = automatic, 1 = system-scope fences, 2 = GPU-scope fences (tuning / diagnosis)
- *   "quant_items_per_sm" work items per SM the quantise kernel aims for (default 4) */
+ * Any other key is rejected with CATCCOS_B200_EINVAL, except the test hooks that
+ * catccos_b200/csrc/internal_options.h lists (they force kernel variants and are not part of this boundary).
+ * The kernels choose their own tiling: CTA pairs (256 x 256 tiles) for more than one wave of work, K cut in
+ * up to eight parts when the tiles would leave half of the SMs idle (the partial tiles meet in a per-rank
+ * scratch allocated when the rank is set up; because of it, and of the symmetric buffer's epochs, the operator
+ * calls of one rank must not overlap on the GPU). */
 int catccos_b200_set_option(const char* key, int64_t value);
 
 /* Number of kernels this library has launched since it was loaded. */

@@ -40,3 +40,7 @@ def test_set_option_rejects_unknown(capi):
     assert capi.load().catccos_b200_set_option(b"no_such_option", 1) == -1
     assert capi.load().catccos_b200_set_option(b"block_n", 192) == -1
     assert capi.load().catccos_b200_set_option(b"block_n", 0) == 0
+    for key in (b"tiny_block_rule", b"c_dtype", b"a_dtype", b"b_dtype"):  # the public keys
+        assert capi.load().catccos_b200_set_option(key, 0) == 0
+        assert capi.load().catccos_b200_set_option(key, 2) == -1
+    assert capi.load().catccos_b200_set_option(b"timeout_ms", 2000) == 0

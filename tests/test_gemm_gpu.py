@@ -24,16 +24,13 @@ def _rand_problem(oracle, m, n, k, seed, a_scale=1.0, dist="normal"):
     return ac, asc, bc, bsc
 
 
-def _run(capi, torch, ac, asc, bc, bsc, block_n=0, b_layout=0, f16=False, cta_pair=2):
+def _run(capi, torch, ac, asc, bc, bsc, block_n=0, f16=False, cta_pair=2):
     capi.set_option("cta_pair", cta_pair)
     capi.set_option("block_n", block_n)
-    capi.set_option("b_layout", b_layout)
     capi.set_option("c_dtype", 1 if f16 else 0)
     try:
         a_d, as_d = torch.from_numpy(ac).cuda(), torch.from_numpy(asc).cuda()
         b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bsc).cuda()
-        if b_layout == 1:
-            b_d = capi.transpose_weight(b_d)
         out = capi.mx_gemm(a_d, as_d, b_d, bs_d, out_dtype=torch.float16 if f16 else torch.bfloat16)
         code, st = capi.last_status()
         assert code == 0, st
@@ -41,7 +38,6 @@ def _run(capi, torch, ac, asc, bc, bsc, block_n=0, b_layout=0, f16=False, cta_pa
     finally:
         capi.set_option("cta_pair", 0)
         capi.set_option("block_n", 0)
-        capi.set_option("b_layout", 0)
         capi.set_option("c_dtype", 0)
 
 
@@ -53,8 +49,7 @@ def _check(oracle, out, gold, k):
 
 
 @pytest.mark.parametrize("block_n", [128, 256])
-@pytest.mark.parametrize("b_layout", [0, 1])
-def test_single_tile_unit_scales(capi, cuda, oracle, block_n, b_layout):
+def test_single_tile_unit_scales(capi, cuda, oracle, block_n):
     # one output tile, one K tile, all scales 1.0: isolates the operand descriptors from the scale path
     rng = np.random.default_rng(1)
     m, n, k = 128, 256, 128
@@ -63,13 +58,12 @@ def test_single_tile_unit_scales(capi, cuda, oracle, block_n, b_layout):
     asc = np.full((m, k // 32), 0x7F, np.uint8)
     bsc = np.full((k // 64, n, 2), 0x7F, np.uint8)
     gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
-    out = _run(capi, cuda, ac, asc, bc, bsc, block_n, b_layout)
+    out = _run(capi, cuda, ac, asc, bc, bsc, block_n)
     _check(oracle, out, gold, k)
 
 
 @pytest.mark.parametrize("block_n", [128, 256])
-@pytest.mark.parametrize("b_layout", [0, 1])
-def test_scale_factor_routing(capi, cuda, oracle, block_n, b_layout):
+def test_scale_factor_routing(capi, cuda, oracle, block_n):
     # every (row, k-block) and (column, k-block) gets its own power of two: a wrong scale-factor
     # layout shows up as errors of a factor of two or more
     rng = np.random.default_rng(2)
@@ -80,7 +74,7 @@ def test_scale_factor_routing(capi, cuda, oracle, block_n, b_layout):
     bs_kn = (118 + (np.arange(k // 32)[:, None] * 5 + np.arange(n)[None, :]) % 11).astype(np.uint8)
     bsc = np.ascontiguousarray(bs_kn.reshape(k // 64, 2, n).transpose(0, 2, 1))
     gold = oracle.allgather_matmul([ac], [asc], bc, bsc)
-    out = _run(capi, cuda, ac, asc, bc, bsc, block_n, b_layout)
+    out = _run(capi, cuda, ac, asc, bc, bsc, block_n)
     _check(oracle, out, gold, k)
 
 
