@@ -316,6 +316,7 @@ def run_gpu(args) -> None:
     align_word = torch.zeros(1, dtype=torch.float32, device=dev)
 
     def timed(fn, steps, warmup, flush_l2=True):
+        barrier()
         for _ in range(warmup):
             fn()
         barrier()
@@ -338,6 +339,7 @@ def run_gpu(args) -> None:
         return ms.cpu().numpy()
 
     warmup = max(args.warmup, 3)
+    barrier()  # the ranks' set-up times differ by more than a device-side wait's limit: start the first call together
     uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
     sampler = ClockSampler("GPU-" + uuid if not uuid.startswith("GPU-") else uuid)
     if rank == 0:
@@ -447,14 +449,24 @@ def run_gpu(args) -> None:
         qa = torch.from_numpy(qa_bits.view(np.int16).copy()).to(dev).view(torch.bfloat16)
         qt = capi.make_tiling(QCFG.m_local, 1, QCFG.k, world)
         qsymm = capi.symm_alloc(capi.symm_bytes_needed(qt, True)) if world > 1 else 0
-        qc = torch.empty((world * QCFG.m_local, QCFG.k), dtype=torch.uint8, device=dev)
-        qs = torch.empty((world * QCFG.m_local, QCFG.k // 32), dtype=torch.uint8, device=dev)
+        nc, ns = world * QCFG.m_local * QCFG.k, world * QCFG.m_local * (QCFG.k // 32)
+        if world > 1:
+            # outputs in symmetric memory (what the operator class allocates): the peers' shards land in them directly
+            ns_off = (nc + 1023) // 1024 * 1024
+            qout = capi.symm_alloc(ns_off + ns)
+            qc = capi.symm_tensor(qout, nc).view(world * QCFG.m_local, QCFG.k)
+            qs = capi.symm_tensor(qout, ns, ns_off).view(world * QCFG.m_local, QCFG.k // 32)
+        else:
+            qc = torch.empty((world * QCFG.m_local, QCFG.k), dtype=torch.uint8, device=dev)
+            qs = torch.empty((world * QCFG.m_local, QCFG.k // 32), dtype=torch.uint8, device=dev)
         q_ms = timed(lambda: capi.mx_quant_allgather(qa, qc, qs, qsymm, world), 20, 3)
         q_us = float(np.median(q_ms)) * 1e3
         qrows = sample_rows(QCFG.m_local, world, seed=99 + rank)
         qrows_t = torch.from_numpy(qrows).to(dev)
         parity.update(check_quant_parity(QCFG, world, qrows, qc[qrows_t].cpu().numpy(), qs[qrows_t].cpu().numpy()))
+        del qc, qs
         if world > 1:
+            capi.symm_free(qout)
             capi.symm_free(qsymm)
         return {
             "workload": f"c2 per rank bf16 [{QCFG.m_local},{QCFG.k}] at world {world}", "us": q_us,

@@ -30,6 +30,7 @@ EXPORTS = [
     "catccos_b200_mx_quant_fp4",
     "catccos_b200_mx_gemm",
     "catccos_b200_mx_quant_matmul_static",
+    "catccos_b200_mx_quant_matmul_static_status",
     "catccos_b200_last_status",
     "catccos_b200_set_option",
     "catccos_b200_launch_count",
@@ -85,6 +86,7 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_mx_gemm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_mx_quant_matmul_static.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_last_status.argtypes = [ctypes.POINTER(u32)]
+    L.catccos_b200_mx_quant_matmul_static_status.argtypes = [ctypes.POINTER(u32)]
     L.catccos_b200_set_option.argtypes = [ctypes.c_char_p, i64]
     L.catccos_b200_launch_count.argtypes = []
     L.catccos_b200_launch_count.restype = ctypes.c_uint64
@@ -122,6 +124,10 @@ def make_tiling(m: int, k: int, n: int, world: int) -> Tiling:
 # ---------------------------------------------------------------------------------------------
 def init(rank: int, world: int, device: int, ip_port: str | None) -> None:
     _check("catccos_b200_init", load().catccos_b200_init(rank, world, device, ip_port.encode() if ip_port else None))
+    # tuning runs: CATCCOS_B200_OPTS="key=value,key=value" sets library options (test hooks included) on every rank
+    for kv in filter(None, os.environ.get("CATCCOS_B200_OPTS", "").split(",")):
+        key, value = kv.split("=", 1)
+        set_option(key.strip(), int(value))
 
 
 def init_local(world: int, devices) -> None:
@@ -143,6 +149,20 @@ def symm_alloc(nbytes: int) -> int:
     return p.value
 
 
+class _DeviceSpan:
+    """A raw device address range in the form torch.as_tensor understands."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def symm_tensor(ptr: int, nbytes: int, offset: int = 0):
+    """A uint8 torch view of [ptr + offset, ptr + offset + nbytes) inside a buffer from symm_alloc (no copy)."""
+    import torch
+
+    return torch.as_tensor(_DeviceSpan(ptr + offset, nbytes), device="cuda")
+
+
 def symm_free(ptr: int) -> None:
     _check("catccos_b200_symm_free", load().catccos_b200_symm_free(ptr))
 
@@ -158,6 +178,13 @@ def set_option(key: str, value: int) -> None:
 def last_status():
     out = (ctypes.c_uint32 * 4)()
     code = load().catccos_b200_last_status(out)
+    return code, tuple(int(v) for v in out)
+
+
+def static_status():
+    """The wait record of the allocation-free entry point's last call on the current device."""
+    out = (ctypes.c_uint32 * 4)()
+    code = load().catccos_b200_mx_quant_matmul_static_status(out)
     return code, tuple(int(v) for v in out)
 
 

@@ -113,6 +113,11 @@ struct RankCtx {
     float* splitk_ws = nullptr;
     uint32_t* splitk_flags = nullptr;
     uint32_t splitk_epoch = 0;
+    // copy-engine allgather: one stream per peer (the transfers to the peers run side by side), an event that
+    // marks "this rank's shard is quantised" and one per stream that marks "everything for that peer has left"
+    cudaStream_t copy[kMaxRanks] = {};
+    cudaEvent_t ev_quant = nullptr;
+    cudaEvent_t ev_copy[kMaxRanks] = {};
 #ifdef CATCCOS_TRACE
     unsigned long long* trace = nullptr;  // [SMs][kTraceSlots] timeline words of the armed launch
     int trace_grid = 0;
@@ -178,6 +183,11 @@ int setup_rank_ctx(RankCtx& rc, int device)
     CUDA_TRY(cudaMalloc(&rc.splitk_flags, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     CUDA_TRY(cudaMemset(rc.splitk_flags, 0, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     rc.splitk_epoch = 0;
+    CUDA_TRY(cudaEventCreateWithFlags(&rc.ev_quant, cudaEventDisableTiming));
+    for (int t = 0; t < kMaxRanks; ++t) {
+        CUDA_TRY(cudaStreamCreateWithFlags(&rc.copy[t], cudaStreamNonBlocking));
+        CUDA_TRY(cudaEventCreateWithFlags(&rc.ev_copy[t], cudaEventDisableTiming));
+    }
 #ifdef CATCCOS_TRACE
     CUDA_TRY(cudaMalloc(&rc.trace, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long)));
     CUDA_TRY(cudaMemset(rc.trace, 0, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long)));
@@ -191,6 +201,11 @@ void destroy_rank_ctx(RankCtx& rc)
     if (rc.status) cudaFree(rc.status);
     if (rc.splitk_ws) cudaFree(rc.splitk_ws);
     if (rc.splitk_flags) cudaFree(rc.splitk_flags);
+    if (rc.ev_quant) cudaEventDestroy(rc.ev_quant);
+    for (int t = 0; t < kMaxRanks; ++t) {
+        if (rc.copy[t]) cudaStreamDestroy(rc.copy[t]);
+        if (rc.ev_copy[t]) cudaEventDestroy(rc.ev_copy[t]);
+    }
 #ifdef CATCCOS_TRACE
     if (rc.trace) cudaFree(rc.trace);
 #endif
@@ -222,6 +237,19 @@ SymmAlloc* find_symm(const void* p)
 {
     for (auto& a : g.allocs) {
         if (a && a->base[g.rank] == p) {
+            return a.get();
+        }
+    }
+    return nullptr;
+}
+
+// The symmetric allocation that holds [p, p + bytes) on the acting rank, and p's offset inside it.
+SymmAlloc* find_symm_containing(const void* p, size_t bytes, size_t* offset)
+{
+    const uint8_t* q = static_cast<const uint8_t*>(p);
+    for (auto& a : g.allocs) {
+        if (a && a->base[g.rank] != nullptr && q >= a->base[g.rank] && q + bytes <= a->base[g.rank] + a->size) {
+            *offset = (size_t)(q - a->base[g.rank]);
             return a.get();
         }
     }
@@ -538,6 +566,68 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     return CATCCOS_B200_EINVAL;
 }
 
+// Ends once every listed flag word carries the epoch (bounded): what follows on the stream may read the rows the
+// peers' copy engines wrote.  One thread per word.
+__global__ void wait_flags_kernel(const uint32_t* flags, uint32_t flag_stride, uint32_t world, uint32_t rank, uint32_t chunks,
+                                  uint32_t segs, uint32_t epoch, uint64_t timeout_ns, StatusBlock* status)
+{
+    const uint32_t slices = (chunks * kRowsPerChunk + 255u) / 256u;
+    const uint32_t n = (world - 1) * slices;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t src = (rank + 1 + i / slices) % world;
+        const uint32_t slice = i % slices;
+        const uint32_t last_chunk = min(chunks, (slice + 1) * (256u / kRowsPerChunk)) - 1u;
+        // the last word a peer's stream writes for the slice: everything before it on that stream has landed
+        const uint32_t* f = flags + (size_t)src * flag_stride + (size_t)last_chunk * segs + (segs - 1u);
+        if (!wait_flag_ge(f, epoch, timeout_ns, status)) {
+            report_status(status, kStatusFlagTimeout, src, last_chunk, epoch);
+        }
+    }
+}
+
+constexpr uint32_t kCopySliceRows = 256;  // rows the copy engines move (and flag) at a time: one row of GEMM tiles
+
+// AllGather of this rank's quantised shard by the copy engines.  Behind the quantise kernel on `st` (an event),
+// one stream per peer copies the shard slice by slice - codes, scales, then the slice's flag words, which the
+// quantise kernel has set to the epoch in this rank's own flag array - into that peer's stage.  Copies of one
+// stream run in order, so a peer sees a slice's flags only after the slice's data; the streams of the seven
+// peers run side by side and share the NVLink egress.  No SM takes part: the GEMM that runs meanwhile keeps
+// its load/store units to itself, and the slices arrive in the order the GEMM visits them.
+int copy_engine_push(RankCtx& rc, cudaStream_t st, uint32_t W, uint32_t rank, uint32_t M, uint32_t K, uint32_t segs,
+                     const uint8_t* src_codes, const uint8_t* src_scales, const uint32_t* src_flags,
+                     uint8_t* const* dst_codes, uint8_t* const* dst_scales, uint32_t* const* dst_flags)
+{
+    const uint32_t sf = K / 32;
+    CUDA_TRY(cudaEventRecord(rc.ev_quant, st));
+    for (uint32_t t = 0; t + 1 < W; ++t) {
+        const uint32_t d = (rank + 1 + t) % W;
+        cudaStream_t cs = rc.copy[t];
+        CUDA_TRY(cudaStreamWaitEvent(cs, rc.ev_quant, 0));
+        for (uint32_t r0 = 0; r0 < M; r0 += kCopySliceRows) {
+            const uint32_t rows = std::min(kCopySliceRows, M - r0);
+            const uint32_t c0 = r0 / kRowsPerChunk, chunks = (rows + kRowsPerChunk - 1) / kRowsPerChunk;
+            CUDA_TRY(cudaMemcpyAsync(dst_codes[d] + (size_t)r0 * K, src_codes + (size_t)r0 * K, (size_t)rows * K,
+                                     cudaMemcpyDeviceToDevice, cs));
+            CUDA_TRY(cudaMemcpyAsync(dst_scales[d] + (size_t)r0 * sf, src_scales + (size_t)r0 * sf, (size_t)rows * sf,
+                                     cudaMemcpyDeviceToDevice, cs));
+            CUDA_TRY(cudaMemcpyAsync(dst_flags[d] + (size_t)c0 * segs, src_flags + (size_t)c0 * segs,
+                                     (size_t)chunks * segs * sizeof(uint32_t), cudaMemcpyDeviceToDevice, cs));
+        }
+        CUDA_TRY(cudaEventRecord(rc.ev_copy[t], cs));
+    }
+    return 0;
+}
+
+// The caller's stream does not run past the call before this rank's shard has left: the next call but one
+// writes the same stage, and the flag words the copies read are rewritten by the very next call.
+int copy_engine_join(RankCtx& rc, cudaStream_t st, uint32_t W)
+{
+    for (uint32_t t = 0; t + 1 < W; ++t) {
+        CUDA_TRY(cudaStreamWaitEvent(st, rc.ev_copy[t], 0));
+    }
+    return 0;
+}
+
 // Common part of the two AllGather-Matmul entry points.
 int allgather_matmul(void* stream, const void* a, const void* a_scale, bool prequant, const void* b,
                      const void* b_scale, void* c, void* symm, const catccos_b200_tiling_t* t)
@@ -650,13 +740,40 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
 
     // With one rank there is no transfer to hide: the quantise kernel uses every SM for a few microseconds and
     // the GEMM follows it on the same stream, which measures faster than sharing the SMs between the two.
-    const int fuse_mode = (g.fuse_mode == 3 && W > 1) ? 0 : (g.fuse_mode >= 0 ? g.fuse_mode : (W == 1 ? 3 : 0));
+    // Several ranks: shards of at least half a MiB per peer travel by the copy engines (mode 5: no SM stores to
+    // NVLink while the GEMM runs, slices arrive in the GEMM's order); smaller ones (decode) are pushed by the
+    // pusher warps of the one fused kernel (mode 0), where a call is one launch and a few microseconds.
+    const bool big_shard = (size_t)M * K >= (512u << 10);
+    const int fuse_mode = W == 1 ? ((g.fuse_mode == 5 || g.fuse_mode < 0) ? 3 : g.fuse_mode)
+                                 : (g.fuse_mode == 3 ? 0 : (g.fuse_mode >= 0 ? g.fuse_mode : (big_shard ? 5 : 0)));
     if (produce && consume && fuse_mode == 3) {
         q.publish = 0;
         rcode = launch_quant_push(rc, st, q, prequant, true);
         if (rcode != 0) return rcode;
         p.flags = nullptr;  // stream order is the only dependency
         return launch_gemm(rc, st, a_stage, b, p, false, true);
+    }
+    if (fuse_mode == 5) {
+        if (produce) {
+            QuantPushParams ql = q;  // the quantise kernel writes this rank's stage and its own flag words only
+            for (uint32_t d = 0; d < W; ++d) {
+                if (d != rank) {
+                    ql.dst_codes[d] = nullptr;
+                    ql.dst_scales[d] = nullptr;
+                    ql.dst_flags[d] = nullptr;
+                }
+            }
+            rcode = launch_quant_push(rc, st, ql, prequant, true, true);
+            if (rcode != 0) return rcode;
+            rcode = copy_engine_push(rc, st, W, rank, M, K, seg.segs_per_chunk, q.dst_codes[rank], q.dst_scales[rank],
+                                     q.dst_flags[rank], q.dst_codes, q.dst_scales, q.dst_flags);
+            if (rcode != 0) return rcode;
+        }
+        if (consume) {
+            rcode = launch_gemm(rc, st, a_stage, b, p);  // gated on the flags, own rows included
+            if (rcode != 0) return rcode;
+        }
+        return produce ? copy_engine_join(rc, st, W) : 0;
     }
     if (produce) {
         // one GEMM launch: quantise warps fill the local stage, pusher warps forward it to the peers, the GEMM
@@ -984,6 +1101,9 @@ int catccos_b200_mx_quant(void* stream, const void* in_bf16, uint32_t rows, uint
     if (((uintptr_t)in_bf16 | (uintptr_t)codes) & 15u) {
         return CATCCOS_B200_EINVAL;
     }
+    if (k % 128 == 0 && ((uintptr_t)scales & 3u)) {
+        return CATCCOS_B200_EINVAL;  // four scale bytes go out as one 32-bit store when a row holds a multiple of four
+    }
     int rcode = ensure_init();
     if (rcode != 0) return rcode;
     RankCtx& rc = cur();
@@ -1043,6 +1163,9 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
     if (((uintptr_t)in_bf16 | (uintptr_t)out_codes) & 15u) {
         return CATCCOS_B200_EINVAL;
     }
+    if (K % 128 == 0 && ((uintptr_t)out_scales & 3u)) {
+        return CATCCOS_B200_EINVAL;  // scales are stored and copied as 32-bit words when a row holds a multiple of four
+    }
     RankCtx& rc = cur();
     CUDA_TRY(cudaSetDevice(rc.device));
     const uint32_t rank = (uint32_t)g.rank;
@@ -1080,28 +1203,58 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
     }
     const uint32_t epoch = sa->epoch[g.rank];
     const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * L.stage_bytes;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* my_flags = reinterpret_cast<uint32_t*>(sa->base[rank] + kFlagsOff);
+    // Outputs that live in symmetric memory (the same offset on every rank) receive the peers' shards directly;
+    // other outputs receive them through this rank's stage and one more local copy.
+    size_t off_c = 0, off_s = 0;
+    SymmAlloc* sc = find_symm_containing(oc, (size_t)W * M * K, &off_c);
+    SymmAlloc* ss = find_symm_containing(os, (size_t)W * M * (K / 32), &off_s);
+    const bool direct = sc != nullptr && ss != nullptr;
+    // the quantise kernel writes this rank's shard into the caller's output and sets this rank's own flag words
     q.epoch = epoch;
     q.publish = 1;
-    for (uint32_t d = 0; d < W; ++d) {
-        if (d == rank) {
-            q.dst_codes[d] = oc + (size_t)rank * M * K;
-            q.dst_scales[d] = os + (size_t)rank * M * (K / 32);
-            q.dst_flags[d] = nullptr;
-        } else {
+    q.dst_codes[rank] = oc + (size_t)rank * M * K;
+    q.dst_scales[rank] = os + (size_t)rank * M * (K / 32);
+    q.dst_flags[rank] = my_flags + (size_t)rank * kMaxFlags;
+    if (produce) {
+        rcode = launch_quant_push(rc, st, q, false, true, true);
+        if (rcode != 0) return rcode;
+        // the copy engines forward it, slice by slice, to every peer: into the peer's output or its stage
+        uint8_t* dc[kMaxRanks] = {};
+        uint8_t* ds[kMaxRanks] = {};
+        uint32_t* df[kMaxRanks] = {};
+        for (uint32_t d = 0; d < W; ++d) {
+            if (d == rank) continue;
             uint8_t* base = sa->base[d] + stage_off;
-            q.dst_codes[d] = base + L.codes_off + (size_t)rank * M * K;
-            q.dst_scales[d] = base + L.scales_off + (size_t)rank * M * (K / 32);
-            q.dst_flags[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
+            dc[d] = (direct ? sc->base[d] + off_c : base + L.codes_off) + (size_t)rank * M * K;
+            ds[d] = (direct ? ss->base[d] + off_s : base + L.scales_off) + (size_t)rank * M * (K / 32);
+            df[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
+        }
+        rcode = copy_engine_push(rc, st, W, rank, M, K, q.segs_per_chunk, q.dst_codes[rank], q.dst_scales[rank],
+                                 q.dst_flags[rank], dc, ds, df);
+        if (rcode != 0) return rcode;
+    }
+    if (consume) {
+        if (direct) {
+            wait_flags_kernel<<<1, 128, 0, st>>>(my_flags, kMaxFlags, W, rank, chunks, q.segs_per_chunk, epoch, g.timeout_ns,
+                                                 rc.status);
+            g_launches++;
+            CUDA_TRY(cudaGetLastError());
+        } else {
+            QuantPushParams qc = q;
+            qc.consume = 1;
+            qc.stage_codes = sa->base[rank] + stage_off + L.codes_off;
+            qc.stage_scales = sa->base[rank] + stage_off + L.scales_off;
+            qc.out_codes = oc;
+            qc.out_scales = os;
+            qc.flags = my_flags;
+            qc.flag_stride = kMaxFlags;
+            rcode = launch_quant_push(rc, st, qc, false, false);
+            if (rcode != 0) return rcode;
         }
     }
-    q.consume = consume ? 1u : 0u;
-    q.stage_codes = sa->base[rank] + stage_off + L.codes_off;
-    q.stage_scales = sa->base[rank] + stage_off + L.scales_off;
-    q.out_codes = oc;
-    q.out_scales = os;
-    q.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
-    q.flag_stride = kMaxFlags;
-    return launch_quant_push(rc, (cudaStream_t)stream, q, false, produce);
+    return produce ? copy_engine_join(rc, st, W) : 0;
 }
 
 int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void* b, const void* a_scale,
@@ -1184,7 +1337,7 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.phase_mask = (int)value;
     } else if (k == CATCCOS_B200_OPT_CTA_PAIR && value >= 0 && value <= 2) {
         g.cta_pair = (int)value;
-    } else if (k == CATCCOS_B200_OPT_FUSE_MODE && (value == -1 || value == 0 || value == 3 || value == 4)) {
+    } else if (k == CATCCOS_B200_OPT_FUSE_MODE && (value == -1 || value == 0 || value == 3 || value == 4 || value == 5)) {
         g.fuse_mode = (int)value;
     } else if (k == CATCCOS_B200_OPT_SPLIT_K && value >= 0 && value <= 8) {
         g.split_k = (int)value;
@@ -1240,6 +1393,10 @@ extern "C" int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_b
         ERROR_LOG("mx_quant_matmul_static: k must be a multiple of 128 and n of 16 (got n=%u k=%u)", n, k);
         return CATCCOS_B200_EINVAL;
     }
+    if ((((uintptr_t)a_bf16 | (uintptr_t)b) & 15u) || ((uintptr_t)c & 31u) || ((uintptr_t)b_scale & 1u)) {
+        ERROR_LOG("mx_quant_matmul_static: a and b must be 16-byte aligned, c 32-byte aligned, b_scale 2-byte aligned");
+        return CATCCOS_B200_EINVAL;  // refused before the shared array or the stream is touched
+    }
     if ((size_t)m * k > kStaticMaxElems) {
         ERROR_LOG("mx_quant_matmul_static: m * k = %zu exceeds the built-in scratch of %zu elements; "
                   "use catccos_b200_mx_quant_allgather_matmul with a buffer from catccos_b200_symm_alloc",
@@ -1257,11 +1414,13 @@ extern "C" int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_b
         // One-time set-up for this device (it is current).  In host code the array's name is only a
         // stand-in; the address a kernel may use comes from the runtime.
         void* p = nullptr;
+        int sms = 0;
         CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
-        CUDA_TRY(cudaDeviceGetAttribute(&sd.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         if (!g.drv.Load()) {
             return CATCCOS_B200_ECUDA;
         }
+        sd.num_sms = sms;  // the state is filled in only once every step of the set-up has succeeded
         sd.ptr = static_cast<uint8_t*>(p);
     }
     RankCtx rc;  // a view for the launcher: nothing is created or owned here
@@ -1351,3 +1510,36 @@ extern "C" int catccos_b200_trace_read(unsigned long long* out, uint32_t max_wor
     return 0;
 }
 #endif
+
+// The device-side wait record of the allocation-free entry point lives in the built-in array too (the regular
+// record belongs to a rank context, which that entry point never creates).  Synchronises the device and copies
+// the 16 bytes out; nothing is allocated.
+extern "C" int catccos_b200_mx_quant_matmul_static_status(uint32_t out[4])
+{
+    if (out == nullptr) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxRanks * 2) {
+        return CATCCOS_B200_EINVAL;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDeviceState& sd = g_static_dev[dev];
+    if (sd.ptr == nullptr) {
+        return CATCCOS_B200_ESTATE;  // no call has been made on this device yet
+    }
+    CUDA_TRY(cudaDeviceSynchronize());
+    StatusBlock sb;
+    CUDA_TRY(cudaMemcpy(&sb, sd.ptr + kStaticStatusOff, sizeof(sb), cudaMemcpyDeviceToHost));
+    out[0] = sb.code;
+    out[1] = sb.rank;
+    out[2] = sb.chunk;
+    out[3] = sb.epoch;
+    if (sb.code != 0) {
+        ERROR_LOG("device wait ran out in mx_quant_matmul_static: code %u rank/barrier %u chunk/stage %u epoch %u", sb.code,
+                  sb.rank, sb.chunk, sb.epoch);
+        return CATCCOS_B200_ETIMEOUT;
+    }
+    return 0;
+}

@@ -11,9 +11,11 @@
 #define CATCCOS_B200_OPT_PHASE_MASK "phase_mask"
 // 0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2), 2 = never
 #define CATCCOS_B200_OPT_CTA_PAIR "cta_pair"
-// -1 = automatic (0 with several ranks, 3 with one); 0 = quantise and pusher warps inside the GEMM kernel (one
-// launch); 3 = one rank only: quantise kernel, then GEMM kernel on the same stream; 4 = quantise kernel into the
-// local stage, then the GEMM kernel whose pusher warps forward the stage to the peers
+// -1 = automatic (3 with one rank; with several, 5 for shards of half a MiB and more per peer, else 0);
+// 0 = quantise and pusher warps inside the GEMM kernel (one launch); 3 = one rank only: quantise kernel, then GEMM
+// kernel on the same stream; 4 = quantise kernel into the local stage, then the GEMM kernel whose pusher warps
+// forward the stage to the peers; 5 = quantise kernel, copy engines forward the stage slice by slice, flag-gated
+// GEMM kernel
 #define CATCCOS_B200_OPT_FUSE_MODE "fuse_mode"
 // 0 = automatic (K is cut in up to eight parts when the output tiles would leave half of the SMs idle),
 // 1 = never, 2..8 = at most that many parts

@@ -148,11 +148,16 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, 
     return t;
 }
 
-// Waits (whole warp) until K segment `seg` of every chunk under gathered rows [m0, m0 + 128) carries the epoch.
-// A lane looks at four rows and polls a flag only for a row that is the first of its (source, chunk) inside
-// the tile, so every flag is polled by exactly one lane.  Returns false (on every lane) when a wait ran out.
-__device__ __forceinline__ bool wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane, uint32_t seg)
+// Waits (whole warp) until K segment `seg0` of every chunk under gathered rows [m0, m0 + 128) carries the epoch,
+// and returns how many K segments from seg0 on are there for ALL of those chunks (0 when the wait ran out): a
+// tile whose rows arrived long ago is checked once, not once per segment.  A lane looks at four rows and polls
+// only for a row that is the first of its (source, chunk) inside the tile, so every chunk is polled by exactly
+// one lane.  The polls are relaxed loads, several in flight; the acquire that orders the data behind the flags
+// is one load per polling lane, on the last flag it counted.
+__device__ __forceinline__ uint32_t wait_rows_ready(const GemmParams& p, uint32_t m0, uint32_t lane, uint32_t seg0)
 {
+    const uint32_t nseg = p.segs - seg0;
+    uint32_t ready = nseg;
     bool ok = true;
     for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t row = m0 + lane * 4 + i;
@@ -166,12 +171,50 @@ __device__ __forceinline__ bool wait_rows_ready(const GemmParams& p, uint32_t m0
             continue;
         }
         const uint32_t chunk = in_src / kRowsPerChunk;
-        if (!wait_flag_ge(p.flags + (size_t)src * p.flag_stride + chunk * p.segs + seg, p.epoch, p.timeout_ns, p.status)) {
-            report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
-            ok = false;
+        const uint32_t* f = p.flags + (size_t)src * p.flag_stride + chunk * p.segs + seg0;
+        uint32_t cnt = 0;
+        uint64_t t0 = 0;
+        uint32_t spins = 0;
+        while (true) {
+            bool stop = false;
+            cnt = 0;
+            for (uint32_t base = 0; base < nseg && !stop; base += 8) {
+                uint32_t v[8];
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) {
+                    v[j] = base + j < nseg ? ld_relaxed_sys(f + base + j) : p.epoch - 1u;
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) {
+                    if (!stop && (int32_t)(v[j] - p.epoch) >= 0) {
+                        ++cnt;
+                    } else {
+                        stop = true;
+                    }
+                }
+            }
+            if (cnt > 0) {
+                break;
+            }
+            if (spins == 0) {
+                t0 = globaltimer_ns();
+            }
+            if ((++spins & 0x1Fu) == 0u) {
+                if (globaltimer_ns() - t0 > p.timeout_ns || status_tripped(p.status)) {
+                    report_status(p.status, kStatusFlagTimeout, src, chunk, p.epoch);
+                    ok = false;
+                    break;
+                }
+                __nanosleep(64);
+            }
         }
+        if (cnt > 0) {
+            (void)ld_acquire_sys(f + cnt - 1);
+        }
+        ready = min(ready, cnt);
     }
-    return __all_sync(0xFFFFFFFFu, ok);
+    ready = __reduce_min_sync(0xFFFFFFFFu, ready);
+    return __all_sync(0xFFFFFFFFu, ok) ? ready : 0u;
 }
 
 __device__ __forceinline__ void st_release_cta_shared(uint32_t* p, uint32_t v)
@@ -316,16 +359,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
             const uint32_t kt0 = ks * kper;
+            uint32_t ready_end = kt0;  // K tiles below this index are known to be there
             for (uint32_t kt = kt0; alive && kt < kt0 + kper; ++kt, ++it) {
-                if (p.flags != nullptr && (kt == kt0 || kt % p.seg_ktiles == 0)) {
+                if (p.flags != nullptr && kt >= ready_end) {
                     const unsigned long long t0 = CATCCOS_TR_NOW();
                     (void)t0;
-                    alive = wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    const uint32_t seg0 = kt / p.seg_ktiles;
+                    const uint32_t nready = wait_rows_ready(p, m0, lane, seg0);
+                    alive = nready != 0u;
+                    ready_end = min((seg0 + nready) * p.seg_ktiles, kt0 + kper);
                     fence_proxy_async_all();
                     if (lane == 0) {
-                        // the scale loaders may go ahead up to the end of this K segment (or of the unit)
-                        const uint32_t seg_end = min((kt / p.seg_ktiles + 1u) * p.seg_ktiles, kt0 + kper);
-                        st_release_cta_shared(gate, it + (seg_end - kt));
+                        // the scale loaders may go ahead as far as the rows are known to be there
+                        st_release_cta_shared(gate, it + (ready_end - kt));
                         CATCCOS_TR_ADD(p.trace, kTrProdFlagWaitNs, CATCCOS_TR_NOW() - t0);
                     }
                 }
@@ -467,7 +513,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t total_it = my_units * kper;
         uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
         uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
-        uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+        uint32_t known_end = 0;  // K-tile iterations below this index have their rows in place
         bool alive = true;
 
         auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
@@ -478,14 +524,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             TileCoord tc = tile_coord(unit - ks * num_tiles, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kGemmBlockM;
             const uint32_t n0 = tc.n_tile * BLOCK_N;
-            if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
-                gated_seq = seq;
-                gated_seg = kt / p.seg_ktiles;
-                // the producer has usually seen this segment's flags already and said so in shared memory
-                if (ld_acquire_cta_shared(gate) <= it) {
+            if (p.flags != nullptr && it >= known_end) {
+                // the producer has usually seen these rows' flags already and said so in shared memory
+                // one lane reads the word for the warp: the producer may be updating it, and the branch below holds
+                // warp-wide operations, so every lane has to take the same side
+                const uint32_t g = __shfl_sync(0xFFFFFFFFu, ld_acquire_cta_shared(gate), 0);
+                if (g > it) {
+                    known_end = g;
+                } else {
                     const unsigned long long t0 = CATCCOS_TR_NOW();
                     (void)t0;
-                    alive = wait_rows_ready(p, m0, lane, gated_seg) && alive;
+                    const uint32_t seg0 = kt / p.seg_ktiles;
+                    const uint32_t nready = wait_rows_ready(p, m0, lane, seg0);
+                    alive = alive && nready != 0u;
+                    known_end = it + (min((seg0 + nready) * p.seg_ktiles, ks * kper + kper) - kt);
                     if (lane == 0) {
                         CATCCOS_TR_ADD(p.trace, kTrSfGateWaitNs + j, CATCCOS_TR_NOW() - t0);
                     }
@@ -743,8 +795,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (threadIdx.x == 0) {
         CATCCOS_TR_STAMP(p.trace, kTrCtaEnd);
     }
+    drain_after_abort(p.status);
     if (warp == 5) {
-        drain_after_abort(p.status);
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }

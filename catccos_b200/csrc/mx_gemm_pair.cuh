@@ -142,14 +142,18 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             TileCoord tc = pair_tile_coord(tile, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
             const uint32_t n0 = tc.n_tile * kPairBlockN + cta * 128u;
+            uint32_t ready_end = 0;  // K tiles below this index are known to be there
             for (uint32_t kt = 0; alive && kt < k_tiles; ++kt, ++it) {
-                if (p.flags != nullptr && kt % p.seg_ktiles == 0) {
+                if (p.flags != nullptr && kt >= ready_end) {
                     const unsigned long long t0 = CATCCOS_TR_NOW();
                     (void)t0;
-                    alive = wait_rows_ready(p, m0, lane, kt / p.seg_ktiles);
+                    const uint32_t seg0 = kt / p.seg_ktiles;
+                    const uint32_t nready = wait_rows_ready(p, m0, lane, seg0);
+                    alive = nready != 0u;
+                    ready_end = min((seg0 + nready) * p.seg_ktiles, k_tiles);
                     fence_proxy_async_all();
                     if (lane == 0) {
-                        st_release_cta_shared(gate, it + (min(kt + p.seg_ktiles, k_tiles) - kt));
+                        st_release_cta_shared(gate, it + (ready_end - kt));
                         CATCCOS_TR_ADD(p.trace, kTrProdFlagWaitNs, CATCCOS_TR_NOW() - t0);
                     }
                 }
@@ -270,7 +274,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t total_it = my_tiles * k_tiles;
         uint32_t cur_a[4], cur_lo[kNB], cur_hi[kNB];
         uint32_t nxt_a[4], nxt_lo[kNB], nxt_hi[kNB];
-        uint32_t gated_seq = 0xFFFFFFFFu, gated_seg = 0xFFFFFFFFu;
+        uint32_t known_end = 0;  // K-tile iterations below this index have their rows in place
         bool alive = true;
 
         auto issue_loads = [&](uint32_t it, uint32_t (&ra)[4], uint32_t (&rlo)[kNB], uint32_t (&rhi)[kNB]) {
@@ -279,14 +283,20 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             TileCoord tc = pair_tile_coord(pair + seq * num_pairs, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
             const uint32_t n0 = tc.n_tile * kPairBlockN;
-            if (p.flags != nullptr && (seq != gated_seq || kt / p.seg_ktiles != gated_seg)) {
-                gated_seq = seq;
-                gated_seg = kt / p.seg_ktiles;
-                // this CTA's producer has usually seen the segment's flags already and said so in shared memory
-                if (ld_acquire_cta_shared(gate) <= it) {
+            if (p.flags != nullptr && it >= known_end) {
+                // this CTA's producer has usually seen these rows' flags already and said so in shared memory
+                // one lane reads the word for the warp: the producer may be updating it, and the branch below holds
+                // warp-wide operations, so every lane has to take the same side
+                const uint32_t g = __shfl_sync(0xFFFFFFFFu, ld_acquire_cta_shared(gate), 0);
+                if (g > it) {
+                    known_end = g;
+                } else {
                     const unsigned long long t0 = CATCCOS_TR_NOW();
                     (void)t0;
-                    alive = wait_rows_ready(p, m0, lane, gated_seg) && alive;
+                    const uint32_t seg0 = kt / p.seg_ktiles;
+                    const uint32_t nready = wait_rows_ready(p, m0, lane, seg0);
+                    alive = alive && nready != 0u;
+                    known_end = it + (min((seg0 + nready) * p.seg_ktiles, k_tiles) - kt);
                     if (lane == 0) {
                         CATCCOS_TR_ADD(p.trace, kTrSfGateWaitNs + j, CATCCOS_TR_NOW() - t0);
                     }
@@ -445,12 +455,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     tcgen05_fence_before();
     __syncthreads();
+    drain_after_abort(p.status);  // both CTAs stay while loads that report to the other's barriers may be in flight
     cluster_sync_all();  // nobody leaves while the other CTA may still arrive on its barriers
     if (threadIdx.x == 0) {
         CATCCOS_TR_STAMP(p.trace, kTrCtaEnd);
     }
     if (warp == 5) {
-        drain_after_abort(p.status);
         tcgen05_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemCols);
     }

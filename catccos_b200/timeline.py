@@ -14,6 +14,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import numpy as np
 
@@ -108,6 +109,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus
+
+    def progress(what):
+        print(f"[timeline rank {rank}] {what}", file=sys.stderr, flush=True)
+
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -120,6 +125,7 @@ def main():
     for kv in args.opt:
         key, val = kv.split("=", 1)
         capi.set_option(key, int(val))
+    progress("library initialised")
 
     cfg = workloads.Config("timeline", args.m, args.k, args.n, (world,), "normal", "")
     a = torch.from_numpy(workloads.activation_bits(cfg, rank, seed=0).view(np.int16).copy()).to(dev).view(torch.bfloat16)
@@ -131,6 +137,7 @@ def main():
     symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(args.m, args.k, args.n, world), False))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     word = torch.zeros(1, device=dev)
+    progress("buffers ready")
 
     def one(timed=False):
         flush.fill_(1)
@@ -144,9 +151,12 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3
 
-    for _ in range(args.warmup):
-        one()
+    for i in range(args.warmup):
+        us = one()
+        if i == 0:
+            progress(f"first step done in {us:.1f} us, status {capi.last_status()}")
     plain = sorted(one() for _ in range(10))
+    progress(f"untraced steps done, p50 {plain[5]:.1f} us")
     if world > 1:
         dist.barrier()
     capi.trace_arm()

@@ -124,10 +124,18 @@ int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const
  * looks up the array's device address (that device must be current) and should therefore be made
  * before any stream capture begins.  All calls on a device share the one array, which keeps the last
  * call's contents: calls are correct back to back on one stream, but two calls whose kernels overlap
- * on the GPU (different streams, no dependency) race on it.  Device-side wait records of this path
- * are not readable through catccos_b200_last_status. */
+ * on the GPU (different streams, no dependency) race on it.  The kernels that the first call of a new shape
+ * class (tile width, output type) launches are configured on that first launch as well, so make one call per
+ * shape class before capture.  Device-side wait records of this path are kept in the same array and read with
+ * catccos_b200_mx_quant_matmul_static_status, not with catccos_b200_last_status. */
 int catccos_b200_mx_quant_matmul_static(void* stream, const void* a_bf16, const void* b, const void* b_scale, void* c,
                                         uint32_t m, uint32_t n, uint32_t k);
+
+/* catccos_b200_last_status for the entry point above: synchronises the current device and copies the 16-byte
+ * record of its last call out of the built-in array (out[] as below).  Allocates nothing.  Returns
+ * CATCCOS_B200_ESTATE before the first call on the device, CATCCOS_B200_ETIMEOUT when a wait ran out.
+ * No counterpart in the reference. */
+int catccos_b200_mx_quant_matmul_static_status(uint32_t out[4]);
 
 /* ---- status and options ---------------------------------------------------------------------
  * out[0] code (0 ok, 1 ready-flag timeout, 2 internal barrier timeout, 3 handshake timeout),

@@ -26,6 +26,7 @@ def local_world(capi, cuda):
     capi.set_option("phase_mask", 3)
     capi.set_option("timeout_ms", 2000)
     capi.set_option("cta_pair", 0)
+    capi.set_option("fuse_mode", -1)
     capi.finalize()
 
 
@@ -51,18 +52,31 @@ def _quant_allgather_round(capi, torch, xs, outs, symm, world):
         assert code == 0, (r, st)
 
 
-@pytest.mark.parametrize("world,m,k", [(2, 64, 1024), (4, 126, 512), (3, 37, 160), (8, 16, 7168)])
-def test_quant_allgather_emulated(capi, cuda, oracle, local_world, world, m, k):
+@pytest.mark.parametrize("symmetric_out", [False, True])
+@pytest.mark.parametrize("world,m,k", [(2, 64, 1024), (4, 126, 512), (3, 37, 160), (8, 16, 7168), (2, 8190, 512)])
+def test_quant_allgather_emulated(capi, cuda, oracle, local_world, world, m, k, symmetric_out):
+    # (2, 8190, 512): the reference's ragged row count (scripts/test_shapes.csv: 8190 = 63 * 128 + 126)
     torch = cuda
     local_world(world)
     t = capi.make_tiling(m, 1, k, world)
     symm = _alloc_symm(capi, world, capi.symm_bytes_needed(t, True))
+    nc, ns = world * m * k, world * m * (k // 32)
+    ns_off = (nc + 1023) // 1024 * 1024
+    out_symm = _alloc_symm(capi, world, ns_off + ns) if symmetric_out else None
     rng = np.random.default_rng(world * 1000 + m)
     for rnd in range(3):  # three rounds: both stages and the reuse of the first
         bits = [workloads.f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)) for _ in range(world)]
         xs = [to_dev_bf16(torch, b) for b in bits]
-        outs = [(torch.full((world * m, k), 0xAA, dtype=torch.uint8, device="cuda"),
-                 torch.full((world * m, k // 32), 0xAA, dtype=torch.uint8, device="cuda")) for _ in range(world)]
+        if symmetric_out:
+            # outputs inside symmetric memory at the same offset on every rank: the peers write them directly
+            outs = [(capi.symm_tensor(out_symm[r], nc).view(world * m, k),
+                     capi.symm_tensor(out_symm[r], ns, ns_off).view(world * m, k // 32)) for r in range(world)]
+            for oc, osc in outs:
+                oc.fill_(0xAA)
+                osc.fill_(0xAA)
+        else:
+            outs = [(torch.full((world * m, k), 0xAA, dtype=torch.uint8, device="cuda"),
+                     torch.full((world * m, k // 32), 0xAA, dtype=torch.uint8, device="cuda")) for _ in range(world)]
         _quant_allgather_round(capi, torch, xs, outs, symm, world)
         want = [oracle.quantize_rows(b) for b in bits]
         want_c = np.concatenate([w[0] for w in want])
@@ -86,13 +100,15 @@ def _agmm_round(capi, torch, call, world):
         assert code == 0, (r, st)
 
 
+@pytest.mark.parametrize("fuse_mode", [0, 5])  # pusher warps of the fused kernel / copy engines
 @pytest.mark.parametrize("cta_pair", [2, 1])
 @pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272),
                                          (2, 16, 7168, 512), (4, 48, 4096, 272)])  # the last two: K split in 8 and 4 parts
-def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n, cta_pair):
+def test_quant_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n, cta_pair, fuse_mode):
     torch = cuda
     local_world(world)
     capi.set_option("cta_pair", cta_pair)
+    capi.set_option("fuse_mode", fuse_mode)
     t = capi.make_tiling(m, k, n, world)
     symm = _alloc_symm(capi, world, capi.symm_bytes_needed(t, False))
     cfg = workloads.Config("t", m, k, n, (world,), "normal", "")
@@ -264,3 +280,36 @@ def test_missing_peer_ends_the_gemm_kernel_quickly(capi, cuda, local_world, cta_
     # rank 0's own rows were computed (all zeros here); nothing was written from accumulators that never filled
     assert torch.all(c[m:] == 7.0)
     assert capi.last_status()[0] == 0
+
+
+@pytest.mark.parametrize("world,cfg_name,ranks_checked", [(8, "c3_prefill", (0, 5)), (4, "c3_prefill", (3,))])
+def test_prefill_shape_at_full_size_emulated(capi, cuda, oracle, local_world, world, cfg_name, ranks_checked):
+    # The benchmark's own shape (per rank A [1024, 7168], B [7168, 2304]) with all ranks hosted on one GPU:
+    # several waves of 256 x 256 tiles per CTA pair, 256-row send groups, seven K segments per chunk.
+    # Sampled rows of every source rank are compared with the oracle.
+    torch = cuda
+    cfg = workloads.CONFIGS[cfg_name]
+    m, k, n = cfg.m_local, cfg.k, cfg.n_local
+    local_world(world)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(capi.make_tiling(m, k, n, world), False))
+    a_bits = [workloads.activation_bits(cfg, r, seed=0) for r in range(world)]
+    a_d = [to_dev_bf16(torch, b) for b in a_bits]
+    w = {r: oracle.quantize_weight(workloads.weight_bits(cfg, r, seed=0)) for r in ranks_checked}
+    b_d = {r: (torch.from_numpy(w[r][0]).cuda(), torch.from_numpy(w[r][1]).cuda()) for r in ranks_checked}
+    c_d = [torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for rnd in range(2):  # both stages of the symmetric buffer
+        for c in c_d:
+            c.zero_()
+        _agmm_round(capi, torch,
+                    lambda r: capi.mx_quant_allgather_matmul(a_d[r], b_d[ranks_checked[0] if r not in b_d else r][0],
+                                                             b_d[ranks_checked[0] if r not in b_d else r][1], c_d[r],
+                                                             symm[r], world), world)
+        rng = np.random.default_rng(rnd)
+        rows = np.sort(np.concatenate([s * m + np.r_[0, 127, 128, 255, 256, m - 1, rng.integers(0, m, 10)] for s in range(world)]))
+        a_rows = np.stack([a_bits[i // m][i % m] for i in rows])
+        ac, asc = oracle.quantize_rows(a_rows)
+        for r in ranks_checked:
+            gold = oracle.gemm_f32(oracle.dequant_rows(ac, asc), oracle.dequant_weight(w[r][0], w[r][1]))
+            out = c_d[r][torch.from_numpy(rows).cuda()].float().cpu().numpy()
+            bad, maxdiff = oracle.check_close(out, gold, 1e-2, 1e-3)
+            assert bad == 0, (rnd, r, bad, maxdiff)

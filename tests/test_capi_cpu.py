@@ -44,3 +44,18 @@ def test_set_option_rejects_unknown(capi):
         assert capi.load().catccos_b200_set_option(key, 0) == 0
         assert capi.load().catccos_b200_set_option(key, 2) == -1
     assert capi.load().catccos_b200_set_option(b"timeout_ms", 2000) == 0
+
+
+def test_misaligned_scale_pointers_are_refused_before_any_launch(capi):
+    # With k % 128 == 0 a row's scale bytes are written four at a time: a scales pointer carved from a byte
+    # pool at an odd offset must come back as EINVAL, not as a misaligned-address fault on the device.
+    # The checks run before the library touches CUDA, so made-up addresses do.
+    L = capi.load()
+    assert L.catccos_b200_mx_quant(None, 0x10000, 8, 128, 0x20000, 0x30001) == -1
+    assert L.catccos_b200_mx_quant(None, 0x10000, 8, 128, 0x20008, 0x30000) == -1  # codes not 16-byte aligned
+    t = capi.make_tiling(8, 1, 128, 1)
+    assert L.catccos_b200_mx_quant_allgather(None, 0x10000, 0x20000, 0x30002, None, ctypes.byref(t), 0) in (-1, -3)
+    st = (ctypes.c_uint32 * 4)()
+    # the allocation-free entry point refuses bad pointers before it touches its shared array
+    assert L.catccos_b200_mx_quant_matmul_static(None, 0x10008, 0x20000, 0x30000, 0x40000, 8, 16, 128) == -1
+    assert st[0] == 0

@@ -32,11 +32,17 @@ def test_static_scratch_matches_regular_entry_point_twice(capi, cuda, oracle):
         want = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         capi.mx_quant_allgather_matmul(a_d, b_d, bs_d, want, symm, 1)
         got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-        before = torch.cuda.memory_allocated()
+        if call == 0:
+            # the first call on a device looks the array's address up and configures the kernels: not measured
+            capi.mx_quant_matmul_static(a_d, b_d, bs_d, got)
+            torch.cuda.synchronize()
+            got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]  # the driver's count: sees any allocation, also one made inside the library
         capi.mx_quant_matmul_static(a_d, b_d, bs_d, got)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
-        code, st = capi.last_status()
+        assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated during the call"
+        code, st = capi.static_status()  # the record of this path, kept in the built-in array
         assert code == 0, st
         # same kernels, same inputs: bit-identical; and within the stated tolerance of the oracle
         assert torch.equal(got, want), f"call {call}: outputs differ"
