@@ -115,6 +115,8 @@ struct RankCtx {
     uint32_t splitk_epoch = 0;
     // copy-engine allgather: one stream per peer (the transfers to the peers run side by side), an event that
     // marks "this rank's shard is quantised" and one per stream that marks "everything for that peer has left"
+    cudaStream_t side = nullptr;  // the quantise-and-push kernel runs here, beside the GEMM on the caller's stream
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaStream_t copy[kMaxRanks] = {};
     cudaEvent_t ev_quant = nullptr;
     cudaEvent_t ev_copy[kMaxRanks] = {};
@@ -157,7 +159,6 @@ struct State {
     int cta_pair = 0;        // 0 = automatic, 1 = always CTA pairs (cta_group::2), 2 = never
     int fuse_mode = -1;      // -1 = automatic, 0 = quantise warps inside the GEMM kernel, 3 = (one rank only) quantise
                              // kernel, then GEMM kernel, 4 = quantise kernel, then GEMM-and-push kernel
-    int push_workers = 0;    // 0 = every pusher warp of the grid, else only the first push_workers
     int a_dtype = 0;         // element type of the A codes (what the quantiser writes, what the GEMM reads): 0 = E4M3, 1 = E5M2
     int b_dtype = 0;         // element type of the B codes the caller passes
     int split_k = 0;         // 0 = automatic, 1 = never split K, 2..8 = split K in that many parts when it fits
@@ -183,6 +184,13 @@ int setup_rank_ctx(RankCtx& rc, int device)
     CUDA_TRY(cudaMalloc(&rc.splitk_flags, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     CUDA_TRY(cudaMemset(rc.splitk_flags, 0, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     rc.splitk_epoch = 0;
+    {
+        int lo = 0, hi = 0;
+        CUDA_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        CUDA_TRY(cudaStreamCreateWithPriority(&rc.side, cudaStreamNonBlocking, hi));
+    }
+    CUDA_TRY(cudaEventCreateWithFlags(&rc.ev_fork, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&rc.ev_join, cudaEventDisableTiming));
     CUDA_TRY(cudaEventCreateWithFlags(&rc.ev_quant, cudaEventDisableTiming));
     for (int t = 0; t < kMaxRanks; ++t) {
         CUDA_TRY(cudaStreamCreateWithFlags(&rc.copy[t], cudaStreamNonBlocking));
@@ -201,6 +209,9 @@ void destroy_rank_ctx(RankCtx& rc)
     if (rc.status) cudaFree(rc.status);
     if (rc.splitk_ws) cudaFree(rc.splitk_ws);
     if (rc.splitk_flags) cudaFree(rc.splitk_flags);
+    if (rc.side) cudaStreamDestroy(rc.side);
+    if (rc.ev_fork) cudaEventDestroy(rc.ev_fork);
+    if (rc.ev_join) cudaEventDestroy(rc.ev_join);
     if (rc.ev_quant) cudaEventDestroy(rc.ev_quant);
     for (int t = 0; t < kMaxRanks; ++t) {
         if (rc.copy[t]) cudaStreamDestroy(rc.copy[t]);
@@ -281,7 +292,7 @@ bool stage_layout(size_t symm_bytes, uint32_t W, uint32_t M, uint32_t K, StageLa
 int quant_grid(const RankCtx& rc)
 {
     int per_sm = 0;
-    const void* fn = (const void*)mx_quant_push_kernel;
+    const void* fn = (const void*)mx_quant_push_kernel<false>;
     // An SM keeps one shared-memory carve-out for all resident CTAs.  The GEMM needs the largest one;
     // asking for the same carve-out here lets quantise CTAs and a GEMM CTA share an SM when the two run
     // as separate kernels.
@@ -300,6 +311,9 @@ int quant_grid(const RankCtx& rc)
     return per_sm * rc.num_sms;
 }
 
+// The ordered quantise-and-push kernel (several ranks, GEMM beside it): per_sm CTAs per SM.
+int launch_quant_push_ordered(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, int per_sm);
+
 uint32_t quant_mode(bool prequant)
 {
     return prequant ? kQuantPreQuantised : (g.tiny_block_rule != 0 ? kQuantDeviceTiny : kQuantGolden);
@@ -309,7 +323,8 @@ uint32_t quant_sys_scope(uint32_t world) { return world > 1 ? 1u : 0u; }
 
 constexpr uint32_t kQuantItemsPerSm = 4;  // work items per SM the quantiser's K-segment choice aims for
 
-void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
+// max_cols (0 = none): an upper bound on the columns of a K segment.
+void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p, uint32_t max_cols = 0)
 {
     const uint32_t chunks = (M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t max_segs = (K + kQuantColsPerWarpStep - 1) / kQuantColsPerWarpStep;
@@ -317,14 +332,19 @@ void choose_segments(uint32_t M, uint32_t K, int num_sms, QuantPushParams& p)
     if (want < 1) want = 1;
     if (want > max_segs) want = max_segs;
     uint32_t seg_cols = (uint32_t)align_up((K + want - 1) / want, kQuantColsPerWarpStep);
+    if (max_cols != 0 && seg_cols > max_cols) {
+        seg_cols = max_cols;
+    }
     p.seg_cols = seg_cols;
     p.segs_per_chunk = (K + seg_cols - 1) / seg_cols;
 }
 
+// max_grid (0 = no limit): an upper bound on the CTAs, for a push that has to leave in item order.
 int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, bool produce,
-                      bool local_only = false)
+                      bool local_only = false, int max_grid = 0)
 {
     int grid = quant_grid(rc);
+    if (max_grid > 0 && grid > max_grid) grid = max_grid;
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     uint32_t items = produce ? chunks * p.segs_per_chunk : 0;
     if (p.consume) {
@@ -339,7 +359,39 @@ int launch_quant_push(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool pre
     p.mode = quant_mode(prequant);
     p.e5m2 = g.a_dtype == 1 ? 1u : 0u;
     p.sys_scope = local_only ? quant_sys_scope(1) : quant_sys_scope(p.world);  // no peer sees these stores directly
-    mx_quant_push_kernel<<<grid, kQuantThreads, 0, st>>>(p);
+    if (grid <= 2 * rc.num_sms && items > (uint32_t)grid) {
+        mx_quant_push_kernel<true><<<grid, kQuantThreads, 0, st>>>(p);
+    } else {
+        mx_quant_push_kernel<false><<<grid, kQuantThreads, 0, st>>>(p);
+    }
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_quant_push_ordered(RankCtx& rc, cudaStream_t st, QuantPushParams& p, bool prequant, int per_sm)
+{
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t items = chunks * p.segs_per_chunk;
+    if (items == 0 || p.seg_cols > kOrderedMaxSteps * kQuantColsPerWarpStep) {
+        return CATCCOS_B200_EINVAL;
+    }
+    static bool carveout_set[kMaxRanks * 2] = {};
+    if (rc.device < kMaxRanks * 2 && !carveout_set[rc.device]) {
+        // the GEMM's CTA, which needs the largest shared-memory carve-out, shares the SM with these CTAs
+        cudaFuncSetAttribute((const void*)mx_quant_push_ordered_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+        carveout_set[rc.device] = true;
+    }
+    uint32_t grid = (uint32_t)(per_sm * rc.num_sms);
+    if (grid > items) grid = items;
+    p.produce = 1u;
+    p.consume = 0u;
+    p.mode = quant_mode(prequant);
+    p.e5m2 = g.a_dtype == 1 ? 1u : 0u;
+    p.sys_scope = 1u;
+    mx_quant_push_ordered_kernel<<<grid, kQuantThreads, 0, st>>>(p);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -389,7 +441,7 @@ int launch_gemm_inst(int grid, cudaStream_t st, const CUtensorMap& ta, const CUt
 
 template <typename OutT, bool FUSED>
 int launch_gemm_pair_inst(int max_pairs_hint, uint32_t tiles, cudaStream_t st, const CUtensorMap& ta,
-                          const CUtensorMap& tb, const GemmParams& p)
+                          const CUtensorMap& tb, const GemmParams& p, bool overlap_predecessor)
 {
     auto kern = mx_gemm_pair_kernel<OutT, FUSED>;
     const int threads = FUSED ? kGemmFusedThreads : kGemmThreads;
@@ -423,7 +475,17 @@ int launch_gemm_pair_inst(int max_pairs_hint, uint32_t tiles, cudaStream_t st, c
     uint32_t pairs = (uint32_t)(dev < kMaxRanks * 2 ? max_clusters[dev] : max_pairs_hint);
     if (pairs > (uint32_t)max_pairs_hint) pairs = (uint32_t)max_pairs_hint;
     if (pairs > tiles) pairs = tiles;
-    kern<<<2 * pairs, threads, PairSmem::kDynamicBytes, st>>>(ta, tb, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = PairSmem::kDynamicBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;  // the cluster shape is the kernel's own (__cluster_dims__)
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap_predecessor ? 1 : 0;
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -506,7 +568,6 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
 #ifdef CATCCOS_TRACE
     if (g.trace_armed && rc.trace != nullptr) {
         g.trace_armed = false;
-        CUDA_TRY(cudaMemsetAsync(rc.trace, 0, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long), st));
         p.trace = p.q.trace = p.push.trace = rc.trace;
     }
 #endif
@@ -528,11 +589,11 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         rc.trace_grid = (int)(2 * std::min(tiles, max_pairs));
 #endif
         if (fused_quant) {
-            return f16 ? launch_gemm_pair_inst<__half, true>((int)max_pairs, tiles, st, pa, pb, p)
-                       : launch_gemm_pair_inst<__nv_bfloat16, true>((int)max_pairs, tiles, st, pa, pb, p);
+            return f16 ? launch_gemm_pair_inst<__half, true>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor)
+                       : launch_gemm_pair_inst<__nv_bfloat16, true>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
         }
-        return f16 ? launch_gemm_pair_inst<__half, false>((int)max_pairs, tiles, st, pa, pb, p)
-                   : launch_gemm_pair_inst<__nv_bfloat16, false>((int)max_pairs, tiles, st, pa, pb, p);
+        return f16 ? launch_gemm_pair_inst<__half, false>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor)
+                   : launch_gemm_pair_inst<__nv_bfloat16, false>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
     }
     CUtensorMap ta, tb;
     int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM);
@@ -571,13 +632,10 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
 __global__ void wait_flags_kernel(const uint32_t* flags, uint32_t flag_stride, uint32_t world, uint32_t rank, uint32_t chunks,
                                   uint32_t segs, uint32_t epoch, uint64_t timeout_ns, StatusBlock* status)
 {
-    const uint32_t slices = (chunks * kRowsPerChunk + 255u) / 256u;
-    const uint32_t n = (world - 1) * slices;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const uint32_t src = (rank + 1 + i / slices) % world;
-        const uint32_t slice = i % slices;
-        const uint32_t last_chunk = min(chunks, (slice + 1) * (256u / kRowsPerChunk)) - 1u;
-        // the last word a peer's stream writes for the slice: everything before it on that stream has landed
+    for (uint32_t i = threadIdx.x; i + 1 < world; i += blockDim.x) {
+        const uint32_t src = (rank + 1 + i) % world;
+        const uint32_t last_chunk = chunks - 1u;
+        // the last word a peer's stream writes: everything before it on that stream has landed
         const uint32_t* f = flags + (size_t)src * flag_stride + (size_t)last_chunk * segs + (segs - 1u);
         if (!wait_flag_ge(f, epoch, timeout_ns, status)) {
             report_status(status, kStatusFlagTimeout, src, last_chunk, epoch);
@@ -588,13 +646,14 @@ __global__ void wait_flags_kernel(const uint32_t* flags, uint32_t flag_stride, u
 constexpr uint32_t kCopySliceRows = 256;  // rows the copy engines move (and flag) at a time: one row of GEMM tiles
 
 // AllGather of this rank's quantised shard by the copy engines.  Behind the quantise kernel on `st` (an event),
-// one stream per peer copies the shard slice by slice - codes, scales, then the slice's flag words, which the
-// quantise kernel has set to the epoch in this rank's own flag array - into that peer's stage.  Copies of one
-// stream run in order, so a peer sees a slice's flags only after the slice's data; the streams of the seven
-// peers run side by side and share the NVLink egress.  No SM takes part: the GEMM that runs meanwhile keeps
-// its load/store units to itself, and the slices arrive in the order the GEMM visits them.
+// one stream per peer copies the shard into that peer's stage: all scales first (they are small), then slice by
+// slice the codes followed by the slice's flag words, which the quantise kernel has set to the epoch in this
+// rank's own flag array.  Copies of one stream run in order, so a peer sees a slice's flags only after the
+// slice's data; the streams of the peers run side by side and share the NVLink egress, which hides the few
+// microseconds every copy costs to start.  No SM takes part: the GEMM that runs meanwhile keeps its load/store
+// units to itself, and the slices arrive in the order the GEMM visits them.
 int copy_engine_push(RankCtx& rc, cudaStream_t st, uint32_t W, uint32_t rank, uint32_t M, uint32_t K, uint32_t segs,
-                     const uint8_t* src_codes, const uint8_t* src_scales, const uint32_t* src_flags,
+                     uint32_t slice_rows, const uint8_t* src_codes, const uint8_t* src_scales, const uint32_t* src_flags,
                      uint8_t* const* dst_codes, uint8_t* const* dst_scales, uint32_t* const* dst_flags)
 {
     const uint32_t sf = K / 32;
@@ -603,12 +662,11 @@ int copy_engine_push(RankCtx& rc, cudaStream_t st, uint32_t W, uint32_t rank, ui
         const uint32_t d = (rank + 1 + t) % W;
         cudaStream_t cs = rc.copy[t];
         CUDA_TRY(cudaStreamWaitEvent(cs, rc.ev_quant, 0));
-        for (uint32_t r0 = 0; r0 < M; r0 += kCopySliceRows) {
-            const uint32_t rows = std::min(kCopySliceRows, M - r0);
+        CUDA_TRY(cudaMemcpyAsync(dst_scales[d], src_scales, (size_t)M * sf, cudaMemcpyDeviceToDevice, cs));
+        for (uint32_t r0 = 0; r0 < M; r0 += slice_rows) {
+            const uint32_t rows = std::min(slice_rows, M - r0);
             const uint32_t c0 = r0 / kRowsPerChunk, chunks = (rows + kRowsPerChunk - 1) / kRowsPerChunk;
             CUDA_TRY(cudaMemcpyAsync(dst_codes[d] + (size_t)r0 * K, src_codes + (size_t)r0 * K, (size_t)rows * K,
-                                     cudaMemcpyDeviceToDevice, cs));
-            CUDA_TRY(cudaMemcpyAsync(dst_scales[d] + (size_t)r0 * sf, src_scales + (size_t)r0 * sf, (size_t)rows * sf,
                                      cudaMemcpyDeviceToDevice, cs));
             CUDA_TRY(cudaMemcpyAsync(dst_flags[d] + (size_t)c0 * segs, src_flags + (size_t)c0 * segs,
                                      (size_t)chunks * segs * sizeof(uint32_t), cudaMemcpyDeviceToDevice, cs));
@@ -651,7 +709,9 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     StageLayout L;
     const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
     QuantPushParams seg = {};
-    choose_segments(M, K, rc.num_sms, seg);  // the same split on every rank and in both kernels
+    // the same split on every rank and in both kernels; with several ranks a work item is at most 2048 columns wide
+    // (what the ordered quantise-and-push kernel keeps in registers)
+    choose_segments(M, K, rc.num_sms, seg, W > 1 ? kOrderedMaxSteps * kQuantColsPerWarpStep : 0u);
     if (!stage_layout(sa->size, W, M, K, L) || (size_t)chunks * seg.segs_per_chunk > kMaxFlags) {
         ERROR_LOG("allgather matmul: symmetric buffer of %zu bytes too small", sa->size);
         return CATCCOS_B200_ENOMEM;
@@ -744,14 +804,59 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
     // NVLink while the GEMM runs, slices arrive in the GEMM's order); smaller ones (decode) are pushed by the
     // pusher warps of the one fused kernel (mode 0), where a call is one launch and a few microseconds.
     const bool big_shard = (size_t)M * K >= (512u << 10);
+    const int auto_mode = 6;
     const int fuse_mode = W == 1 ? ((g.fuse_mode == 5 || g.fuse_mode < 0) ? 3 : g.fuse_mode)
-                                 : (g.fuse_mode == 3 ? 0 : (g.fuse_mode >= 0 ? g.fuse_mode : (big_shard ? 5 : 0)));
+                                 : (g.fuse_mode == 3 ? 0 : (g.fuse_mode >= 0 ? g.fuse_mode : (big_shard ? auto_mode : 0)));
     if (produce && consume && fuse_mode == 3) {
         q.publish = 0;
         rcode = launch_quant_push(rc, st, q, prequant, true);
         if (rcode != 0) return rcode;
         p.flags = nullptr;  // stream order is the only dependency
         return launch_gemm(rc, st, a_stage, b, p, false, true);
+    }
+    if (fuse_mode == 6) {
+        // Two kernels on the caller's stream.  The quantise kernel stores every work item to all ranks (one pass:
+        // quantise and allgather) and flags it; the flag-gated GEMM kernel follows (with programmatic stream
+        // serialisation: it may set itself up while the quantise kernel drains).  The quantise grid shrinks with
+        // the number of ranks so that about the same number of bytes is on its way at any time.
+        if (produce) {
+            const int cap = std::max(rc.num_sms, (4 * rc.num_sms) / (int)std::max(1u, W - 1u) / rc.num_sms * rc.num_sms);
+            rcode = launch_quant_push(rc, st, q, prequant, true, false, cap);
+            if (rcode != 0) return rcode;
+        }
+        if (consume) {
+            return launch_gemm(rc, st, a_stage, b, p, false, produce);
+        }
+        return 0;
+    }
+    if (fuse_mode == 7) {
+        // Two kernels side by side.  The ordered quantise-and-push kernel (mx_quant.cuh), on a side stream of high
+        // priority, one CTA per SM, never waits for anybody; the GEMM kernel, launched after it on the caller's
+        // stream, takes one CTA per SM beside it and follows the flags, its own rows included.
+        if (produce && consume) {
+            CUDA_TRY(cudaEventRecord(rc.ev_fork, st));
+            CUDA_TRY(cudaStreamWaitEvent(rc.side, rc.ev_fork, 0));
+        }
+        if (produce) {
+#ifdef CATCCOS_TRACE
+            if (g.trace_armed && rc.trace != nullptr) {
+                q.trace = rc.trace;
+            }
+#endif
+            rcode = launch_quant_push_ordered(rc, consume ? rc.side : st, q, prequant, 1);
+            if (rcode != 0) return rcode;
+            if (consume) {
+                CUDA_TRY(cudaEventRecord(rc.ev_join, rc.side));
+            }
+        }
+        if (consume) {
+            rcode = launch_gemm(rc, st, a_stage, b, p);
+            if (rcode != 0) return rcode;
+            if (produce) {
+                CUDA_TRY(cudaStreamWaitEvent(st, rc.ev_join, 0));
+            }
+        }
+        return 0;
     }
     if (fuse_mode == 5) {
         if (produce) {
@@ -765,8 +870,8 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
             }
             rcode = launch_quant_push(rc, st, ql, prequant, true, true);
             if (rcode != 0) return rcode;
-            rcode = copy_engine_push(rc, st, W, rank, M, K, seg.segs_per_chunk, q.dst_codes[rank], q.dst_scales[rank],
-                                     q.dst_flags[rank], q.dst_codes, q.dst_scales, q.dst_flags);
+            rcode = copy_engine_push(rc, st, W, rank, M, K, seg.segs_per_chunk, kCopySliceRows, q.dst_codes[rank],
+                                     q.dst_scales[rank], q.dst_flags[rank], q.dst_codes, q.dst_scales, q.dst_flags);
             if (rcode != 0) return rcode;
         }
         if (consume) {
@@ -810,7 +915,6 @@ int allgather_matmul(void* stream, const void* a, const void* a_scale, bool preq
         ps.group_chunks = q.group_chunks;
         ps.seg_order_n = q.seg_order_n;
         memcpy(ps.seg_order, q.seg_order, sizeof(ps.seg_order));
-        ps.max_workers = (uint32_t)g.push_workers;
         ps.timeout_ns = g.timeout_ns;
         ps.status = rc.status;
         if (quant_first) {
@@ -1231,7 +1335,9 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
             ds[d] = (direct ? ss->base[d] + off_s : base + L.scales_off) + (size_t)rank * M * (K / 32);
             df[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
         }
-        rcode = copy_engine_push(rc, st, W, rank, M, K, q.segs_per_chunk, q.dst_codes[rank], q.dst_scales[rank],
+        // nobody consumes this operator's rows early: four large slices per peer keep the copies long
+        const uint32_t slice_rows = std::max(kCopySliceRows, (uint32_t)align_up((M + 3) / 4, kCopySliceRows));
+        rcode = copy_engine_push(rc, st, W, rank, M, K, q.segs_per_chunk, slice_rows, q.dst_codes[rank], q.dst_scales[rank],
                                  q.dst_flags[rank], dc, ds, df);
         if (rcode != 0) return rcode;
     }
@@ -1337,12 +1443,10 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.phase_mask = (int)value;
     } else if (k == CATCCOS_B200_OPT_CTA_PAIR && value >= 0 && value <= 2) {
         g.cta_pair = (int)value;
-    } else if (k == CATCCOS_B200_OPT_FUSE_MODE && (value == -1 || value == 0 || value == 3 || value == 4 || value == 5)) {
+    } else if (k == CATCCOS_B200_OPT_FUSE_MODE && (value == -1 || value == 0 || (value >= 3 && value <= 7))) {
         g.fuse_mode = (int)value;
     } else if (k == CATCCOS_B200_OPT_SPLIT_K && value >= 0 && value <= 8) {
         g.split_k = (int)value;
-    } else if (k == CATCCOS_B200_OPT_PUSH_WORKERS && value >= 0 && value <= 65536) {
-        g.push_workers = (int)value;
     } else {
         ERROR_LOG("set_option: unknown key or bad value: %s = %lld", key, (long long)value);
         return CATCCOS_B200_EINVAL;
@@ -1488,6 +1592,13 @@ extern "C" int catccos_b200_trace_arm(void)
     if (g.mode == Mode::kNone) {
         return CATCCOS_B200_ESTATE;
     }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemset(rc.trace, 0, (size_t)rc.num_sms * kTraceSlots * sizeof(unsigned long long)));
+    // the stand-alone quantise kernel keeps the minimum of its CTAs' start times in this word
+    const unsigned long long big = ~0ull;
+    CUDA_TRY(cudaMemcpy(rc.trace + kTrQuantKernelStart, &big, sizeof(big), cudaMemcpyHostToDevice));
     g.trace_armed = true;
     return 0;
 }

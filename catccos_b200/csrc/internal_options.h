@@ -11,14 +11,14 @@
 #define CATCCOS_B200_OPT_PHASE_MASK "phase_mask"
 // 0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2), 2 = never
 #define CATCCOS_B200_OPT_CTA_PAIR "cta_pair"
-// -1 = automatic (3 with one rank; with several, 5 for shards of half a MiB and more per peer, else 0);
+// -1 = automatic (3 with one rank; with several, 6 for shards of half a MiB and more per peer, else 0);
 // 0 = quantise and pusher warps inside the GEMM kernel (one launch); 3 = one rank only: quantise kernel, then GEMM
 // kernel on the same stream; 4 = quantise kernel into the local stage, then the GEMM kernel whose pusher warps
 // forward the stage to the peers; 5 = quantise kernel, copy engines forward the stage slice by slice, flag-gated
-// GEMM kernel
+// GEMM kernel; 6 = quantise kernel that stores every item to all ranks, flag-gated GEMM kernel launched behind it
+// with programmatic stream serialisation; 7 = the ordered quantise-and-push kernel on a side stream, the flag-gated
+// GEMM kernel beside it
 #define CATCCOS_B200_OPT_FUSE_MODE "fuse_mode"
 // 0 = automatic (K is cut in up to eight parts when the output tiles would leave half of the SMs idle),
 // 1 = never, 2..8 = at most that many parts
 #define CATCCOS_B200_OPT_SPLIT_K "split_k"
-// 0 = every pusher warp of the grid forwards work items to the peers, else only the first N of them
-#define CATCCOS_B200_OPT_PUSH_WORKERS "push_workers"

@@ -304,6 +304,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* red_bar = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
     uint32_t* gate = reinterpret_cast<uint32_t*>(smem + S::kOffGate);
+    uint32_t* push_turn = gate + 1;  // the pushers of this CTA store one after the other (mx_quant.cuh, push_worker)
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -329,6 +330,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(&red_bar[w], 1);
         }
         *gate = 0u;
+        *push_turn = 0u;
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -347,7 +349,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (warp == 4) {
         // ------------------------------- TMA producer -------------------------------------
-        grid_dep_wait();  // A may be the output of the kernel launched just before (no-op for a plain launch)
+        if (p.flags == nullptr) {
+            grid_dep_wait();  // A is the output of the kernel launched just before (no-op for a plain launch);
+        }                     // with flags, the flags say when its rows are there
         const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
         const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
         const uint32_t num_units = num_tiles * ksplit;
@@ -494,7 +498,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
             // pusher pw of CTA b is worker pw * grid + b: a short item list spreads over all SMs instead of
             // filling the first CTAs' six pushers
-            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw);
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw, gridDim.x, push_turn);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders ------------------------------------
@@ -504,7 +508,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // scales of a 64-deep K group together), and stores them as 16-byte atom rows.
         constexpr uint32_t kNB = BLOCK_N / 32;  // B words per lane
         const uint32_t j = warp - 6;
-        grid_dep_wait();  // the A scales may be the output of the kernel launched just before
+        if (p.flags == nullptr) {
+            grid_dep_wait();  // the A scales are the output of the kernel launched just before (or: see the flags)
+        }
         const uint32_t sf_row_bytes = p.K / 32;
         const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
         const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)

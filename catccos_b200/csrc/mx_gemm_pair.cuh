@@ -90,6 +90,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* atoms_written = overlap_free + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + S::kOffTmemPtr);
     uint32_t* gate = reinterpret_cast<uint32_t*>(smem + S::kOffGate);
+    uint32_t* push_turn = gate + 1;  // the pushers of this CTA store one after the other (mx_quant.cuh, push_worker)
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -106,6 +107,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (threadIdx.x == 0) {
         CATCCOS_TR_STAMP(p.trace, kTrCtaStart);
         *gate = 0u;
+        *push_turn = 0u;
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 3);  // both CTAs' producers (expect_tx) and the commit behind the scale copies
             mbar_init(&empty[s], 1);
@@ -136,6 +138,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     if (warp == 4) {
         // ------------------------------- TMA producer (both CTAs) -------------------------
+        if (p.flags == nullptr) {
+            grid_dep_wait();  // A is the output of the kernel launched just before (no-op for a plain launch);
+        }                     // with flags, the flags say when its rows are there
         uint32_t it = 0, ti = 0;
         bool alive = true;
         for (uint32_t tile = pair; alive && tile < num_tiles; tile += num_pairs, ++ti) {
@@ -262,13 +267,16 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             quant_push_producer<true>(p.q, qw * 32u + lane, blockIdx.x, gridDim.x, 1);
         } else {
             const uint32_t pw = warp == 13u ? 0u : (warp == 17u ? 1u : warp - 18u);  // 0..5
-            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw);  // spread over all SMs
+            push_worker(p.push, lane, pw * gridDim.x + blockIdx.x, gridDim.x * kPushWarps, pw, gridDim.x, push_turn);
         }
     } else if (warp >= 6) {
         // ------------------------------- scale loaders (both CTAs) ------------------------
         // A scales of this CTA's 128 rows; B scales of all 256 columns of the pair's tile.
         constexpr uint32_t kNB = kPairBlockN / 32;
         const uint32_t j = warp - 6;
+        if (p.flags == nullptr) {
+            grid_dep_wait();  // the A scales are the output of the kernel launched just before (or: see the flags)
+        }
         const uint32_t sf_row_bytes = p.K / 32;
         const uint32_t my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
         const uint32_t total_it = my_tiles * k_tiles;

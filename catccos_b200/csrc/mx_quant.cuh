@@ -326,7 +326,6 @@ struct PushParams {
     uint32_t M, K, rank, world, epoch;
     uint32_t segs_per_chunk, seg_cols, group_chunks, seg_order_n;
     uint8_t seg_order[32];
-    uint32_t max_workers;       // 0, or: only the first max_workers pusher warps of the grid take part
     uint64_t timeout_ns;
     StatusBlock* status;
     unsigned long long* trace;  // timeline side buffer (trace build only), else nullptr
@@ -338,26 +337,27 @@ struct PushParams {
 // 16 rows x one K segment in passes of 4 KiB: eight 16-byte loads in flight per lane, each value stored to
 // every peer (the local stage is read once, whatever the number of ranks; the peers are visited starting
 // behind this rank so that the ranks of a box do not all store to the same GPU at the same moment).  One
-// system-scope fence per item orders the stores before the peers' flag words.  `pw` names the pusher inside
-// its CTA (timeline only).
+// system-scope fence per item orders the stores before the peers' flag words.
+//
+// The pushers of a CTA take turns (`turn`, a word in shared memory that counts the CTA's items): a pusher loads
+// its item's first pass, waits until the item before it has been stored, fenced and flagged, and then does the
+// same.  Every CTA thus feeds NVLink one item after the other, in item order, and all CTAs together keep about
+// one bandwidth-delay product in flight.  When all pushers fire at once instead, the link delivers all items at
+// the same slow pace and the first rows the GEMM needs arrive with the last.
+// `pw` names the pusher inside its CTA, `grid` is the number of CTAs (worker = pw * grid + CTA index).
 __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, uint32_t worker, uint32_t num_workers,
-                                            uint32_t pw)
+                                            uint32_t pw, uint32_t grid, uint32_t* turn)
 {
     (void)pw;
     if (p.world < 2) {
         return;
-    }
-    if (p.max_workers != 0u) {
-        if (worker >= p.max_workers) {
-            return;
-        }
-        num_workers = min(num_workers, p.max_workers);
     }
     const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
     const uint32_t items = chunks * p.segs_per_chunk;
     const uint32_t peers = p.world - 1;
     const uint32_t sf_cols = p.K / 32;
     for (uint32_t item = worker; item < items; item += num_workers) {
+        const uint32_t seq = item / grid;  // this item's place among the CTA's items
         uint32_t chunk, seg;
         item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
         const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
@@ -386,9 +386,9 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
         // codes: rows x cols bytes, 16 bytes per lane per step, eight steps in flight
         const uint32_t per_row = cols / 16;
         const uint32_t n16 = rows * per_row;
-        for (uint32_t i = lane; i < n16; i += 256) {
-            uint4 v[8];
-            size_t off[8];
+        uint4 v[8];
+        size_t off[8];
+        auto load_pass = [&](uint32_t i) {
 #pragma unroll
             for (uint32_t j = 0; j < 8; ++j) {
                 const uint32_t e = i + j * 32;
@@ -397,6 +397,31 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
                 if (e < n16) {
                     v[j] = __ldcg(reinterpret_cast<const uint4*>(p.src_codes + off[j]));
                 }
+            }
+        };
+        load_pass(lane);  // the first pass travels while this pusher waits for its turn
+        if (turn != nullptr) {
+            bool ok = true;
+            if (lane == 0) {
+                const uint64_t t0 = globaltimer_ns();
+                uint32_t spins = 0;
+                while (*reinterpret_cast<volatile uint32_t*>(turn) != seq) {
+                    if ((++spins & 0x3Fu) == 0u) {
+                        if (globaltimer_ns() - t0 > p.timeout_ns || status_tripped(p.status)) {
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                }
+            }
+            if (!__all_sync(0xFFFFFFFFu, ok)) {
+                return;  // an earlier pusher of this CTA gave up
+            }
+        }
+        for (uint32_t i = lane; i < n16; i += 256) {
+            if (i != lane) {
+                load_pass(i);
             }
             for (uint32_t t = 0; t < peers; ++t) {
                 uint8_t* dst = p.dst_codes[(p.rank + 1 + t) % p.world];
@@ -414,19 +439,19 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
             const uint32_t w_per_row = sf_per_row / 4;
             for (uint32_t e = lane; e < rows * w_per_row; e += 32) {
                 const uint32_t r = e / w_per_row;
-                const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (size_t)(e - r * w_per_row) * 4;
-                const uint32_t w = __ldcg(reinterpret_cast<const uint32_t*>(p.src_scales + off));
+                const size_t so = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (size_t)(e - r * w_per_row) * 4;
+                const uint32_t w = __ldcg(reinterpret_cast<const uint32_t*>(p.src_scales + so));
                 for (uint32_t t = 0; t < peers; ++t) {
-                    *reinterpret_cast<uint32_t*>(p.dst_scales[(p.rank + 1 + t) % p.world] + off) = w;
+                    *reinterpret_cast<uint32_t*>(p.dst_scales[(p.rank + 1 + t) % p.world] + so) = w;
                 }
             }
         } else {
             for (uint32_t e = lane; e < rows * sf_per_row; e += 32) {
                 const uint32_t r = e / sf_per_row;
-                const size_t off = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (e - r * sf_per_row);
-                const uint8_t b = __ldcg(p.src_scales + off);
+                const size_t so = (size_t)(r_begin + r) * sf_cols + c_begin / 32 + (e - r * sf_per_row);
+                const uint8_t b = __ldcg(p.src_scales + so);
                 for (uint32_t t = 0; t < peers; ++t) {
-                    p.dst_scales[(p.rank + 1 + t) % p.world][off] = b;
+                    p.dst_scales[(p.rank + 1 + t) % p.world][so] = b;
                 }
             }
         }
@@ -441,16 +466,40 @@ __device__ __forceinline__ void push_worker(const PushParams& p, uint32_t lane, 
                              "r"(p.epoch)
                              : "memory");
             }
+            if (turn != nullptr) {
+                // The turn passes on only now.  A fence waits for the stores the whole SM has in flight, not only
+                // for this warp's: were the next item's stores let out before it, this item's flags would wait
+                // for them too, and so on down the line, and every flag would arrive with the last item.
+                *reinterpret_cast<volatile uint32_t*>(turn) = seq + 1u;
+            }
             CATCCOS_TR_ADD(p.trace, kTrPushItems + pw, 1ull);
             CATCCOS_TR_STAMP(p.trace, kTrPushLast + pw);
         }
     }
 }
 
+// kPrefetch: see quant_push_producer; chosen by the host when only one or two CTAs run per SM (a grid cut down so
+// that the items of a multi-rank push leave in order) and every CTA works through several items.
+template <bool kPrefetch>
 __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushParams p)
 {
     grid_dep_launch();  // a GEMM launched behind this kernel may set itself up while the quantiser drains
-    quant_push_producer<false>(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
+#ifdef CATCCOS_TRACE
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        atomicMin(p.trace + kTrQuantKernelStart, globaltimer_ns());
+    }
+    QuantPushParams pq = p;
+    pq.trace = nullptr;  // the per-CTA rows belong to the GEMM kernel's CTAs
+    quant_push_producer<kPrefetch>(pq, threadIdx.x, blockIdx.x, gridDim.x, 0);
+    if (p.trace != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            atomicMax(p.trace + kTrQuantKernelEnd, globaltimer_ns());
+        }
+    }
+#else
+    quant_push_producer<kPrefetch>(p, threadIdx.x, blockIdx.x, gridDim.x, 0);
+#endif
 
     if (!p.consume) {
         return;
@@ -499,6 +548,168 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_push_kernel(QuantPushP
         }
         __syncthreads();
     }
+}
+
+// The quantise-and-push kernel for several ranks when the GEMM runs beside it: one CTA per SM (or two) works through
+// its items strictly one after the other, and for every item
+//   1. has all of the item's input in flight at once (up to sixteen 16-byte loads per lane: one trip to HBM),
+//   2. quantises, and requests the next item's input before it stores anything,
+//   3. stores the item to this rank's own stage, fences at GPU scope and sets the local flag - the GEMM's tiles
+//      over this rank's own rows can start while the item is still on its way to the peers,
+//   4. stores the same registers to every peer, fences at system scope and sets the peers' flags.
+// A fence waits for the stores the whole SM has in flight, so an SM that keeps one item in flight publishes
+// each item as soon as that item has landed; all SMs together keep about one bandwidth-delay product of NVLink
+// busy, and the items arrive in item order (the rows of the GEMM's first wave first).
+// Needs seg_cols <= kOrderedMaxSteps * 512 (the host caps the K segments accordingly).
+constexpr uint32_t kOrderedMaxSteps = 4;
+
+// (launch bounds: at most 128 registers per thread, so that this CTA and the GEMM's CTA fit one SM's register file)
+__global__ void __launch_bounds__(kQuantThreads, 2) mx_quant_push_ordered_kernel(QuantPushParams p)
+{
+    grid_dep_launch();
+#ifdef CATCCOS_TRACE
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        atomicMin(p.trace + kTrQuantKernelStart, globaltimer_ns());
+    }
+#endif
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t chunks = (p.M + kQuantRowsPerItem - 1) / kQuantRowsPerItem;
+    const uint32_t items = p.produce ? chunks * p.segs_per_chunk : 0u;
+    const uint32_t sf_cols = p.K / 32;
+    const bool sf_vec = (sf_cols % 4u) == 0u;
+    const bool prequant = p.mode == kQuantPreQuantised;
+    const bool device_tiny = p.mode == kQuantDeviceTiny;
+    const bool e5m2 = p.e5m2 != 0u;
+
+    uint4 in[kOrderedMaxSteps][2][2];
+    auto load_item = [&](uint32_t item) {
+        uint32_t chunk, seg;
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
+        const uint32_t c_begin = seg * p.seg_cols;
+        const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
+        const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
+#pragma unroll
+        for (uint32_t st = 0; st < kOrderedMaxSteps; ++st) {
+            const uint32_t col = c_begin + st * kQuantColsPerWarpStep + lane * 16;
+#pragma unroll
+            for (uint32_t r = 0; r < 2; ++r) {
+                const uint32_t row = row0 + r;
+                in[st][r][0] = in[st][r][1] = make_uint4(0, 0, 0, 0);
+                if (col < c_end && row < p.M) {
+                    if (prequant) {
+                        in[st][r][0] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.in) +
+                                                                            (size_t)row * p.K + col));
+                    } else {
+                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.in) +
+                                                                          (size_t)row * p.K + col);
+                        in[st][r][0] = __ldcs(src);
+                        in[st][r][1] = __ldcs(src + 1);
+                    }
+                }
+            }
+        }
+    };
+
+    uint32_t item = blockIdx.x;
+    if (item < items) {
+        load_item(item);
+    }
+    for (; item < items; item += gridDim.x) {
+        uint32_t chunk, seg;
+        item_coord(item, chunks, p.segs_per_chunk, p.group_chunks, p.seg_order, p.seg_order_n, chunk, seg);
+        const uint32_t c_begin = seg * p.seg_cols;
+        const uint32_t c_end = min(p.K, c_begin + p.seg_cols);
+        const uint32_t row0 = chunk * kQuantRowsPerItem + warp * 2;
+        const uint32_t flag_index = chunk * p.segs_per_chunk + seg;
+
+        uint4 o[kOrderedMaxSteps][2];
+        uint32_t w[kOrderedMaxSteps][2], byte[kOrderedMaxSteps][2];
+#pragma unroll
+        for (uint32_t st = 0; st < kOrderedMaxSteps; ++st) {
+            const uint32_t col = c_begin + st * kQuantColsPerWarpStep + lane * 16;
+#pragma unroll
+            for (uint32_t r = 0; r < 2; ++r) {
+                const uint32_t row = row0 + r;
+                if (prequant) {
+                    o[st][r] = in[st][r][0];
+                    byte[st][r] = 0;
+                    if (col < c_end && row < p.M && (lane & 1u) == 0u) {
+                        byte[st][r] = p.in_scales[(size_t)row * sf_cols + col / 32];
+                    }
+                } else {
+                    o[st][r] = quant16(in[st][r][0], in[st][r][1], device_tiny, e5m2, byte[st][r]);
+                }
+                const uint32_t base = lane & ~7u;
+                w[st][r] = __shfl_sync(0xFFFFFFFFu, byte[st][r], base) | (__shfl_sync(0xFFFFFFFFu, byte[st][r], base + 2) << 8) |
+                           (__shfl_sync(0xFFFFFFFFu, byte[st][r], base + 4) << 16) |
+                           (__shfl_sync(0xFFFFFFFFu, byte[st][r], base + 6) << 24);
+            }
+        }
+        if (item + gridDim.x < items) {
+            load_item(item + gridDim.x);  // travels while this item is stored, fenced and flagged
+        }
+        auto store_to = [&](uint32_t d) {
+#pragma unroll
+            for (uint32_t st = 0; st < kOrderedMaxSteps; ++st) {
+                const uint32_t col = c_begin + st * kQuantColsPerWarpStep + lane * 16;
+#pragma unroll
+                for (uint32_t r = 0; r < 2; ++r) {
+                    const uint32_t row = row0 + r;
+                    if (col < c_end && row < p.M) {
+                        *reinterpret_cast<uint4*>(p.dst_codes[d] + (size_t)row * p.K + col) = o[st][r];
+                        const size_t sf_off = (size_t)row * sf_cols + col / 32;
+                        if (sf_vec) {
+                            if ((lane & 7u) == 0u) {
+                                *reinterpret_cast<uint32_t*>(p.dst_scales[d] + sf_off) = w[st][r];
+                            }
+                        } else if ((lane & 1u) == 0u) {
+                            p.dst_scales[d][sf_off] = (uint8_t)byte[st][r];
+                        }
+                    }
+                }
+            }
+        };
+        // this rank's own stage first: its rows are the first the GEMM beside this kernel works on
+        if (p.rank < p.num_dst && p.dst_codes[p.rank] != nullptr) {
+            store_to(p.rank);
+            __syncthreads();
+            if (tid == 0 && p.dst_flags[p.rank] != nullptr) {
+                __threadfence();
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[p.rank] + flag_index), "r"(p.epoch)
+                             : "memory");
+            }
+        }
+        // then the peers, starting behind this rank so that the ranks of a box do not all store to the same GPU
+        bool any_peer = false;
+        for (uint32_t t = 1; t < p.num_dst; ++t) {
+            const uint32_t d = (p.rank + t) % p.num_dst;
+            if (p.dst_codes[d] != nullptr) {
+                store_to(d);
+                any_peer = true;
+            }
+        }
+        if (any_peer) {
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();
+                for (uint32_t t = 1; t < p.num_dst; ++t) {
+                    const uint32_t d = (p.rank + t) % p.num_dst;
+                    if (p.dst_flags[d] != nullptr) {
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.dst_flags[d] + flag_index), "r"(p.epoch)
+                                     : "memory");
+                    }
+                }
+            }
+        }
+    }
+#ifdef CATCCOS_TRACE
+    if (p.trace != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            atomicMax(p.trace + kTrQuantKernelEnd, globaltimer_ns());
+        }
+    }
+#endif
 }
 
 // bf16 [rows, K] -> FP4 E2M1 codes, two per byte (low nibble = even column), + one E8M0 scale per 32 elements.

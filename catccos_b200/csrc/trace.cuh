@@ -42,6 +42,8 @@ enum TraceSlot : uint32_t {
     kTrSfGateWaitNs = 64,   // + scale-loader index: time waiting for ready flags
     kTrSfEmptyWaitNs = 68,  // + scale-loader index: time waiting for a free stage
     kTrCtaEnd = 72,
+    kTrQuantKernelStart = 73,  // row 0 only: earliest CTA start of the stand-alone quantise kernel (atomic min)
+    kTrQuantKernelEnd = 74,    // row 0 only: latest CTA end of the stand-alone quantise kernel (atomic max)
 };
 
 #ifdef CATCCOS_TRACE

@@ -53,6 +53,9 @@ def summarise(tr: np.ndarray) -> dict:
         return (v[v > 0].astype(np.float64) - float(t0)) / 1e3
 
     out["CTA start"] = _mmm(rel(0))
+    qs, qe = int(tr[0, 73]), int(tr[0, 74])
+    if qe > 0 and qs != 0xFFFFFFFFFFFFFFFF:
+        out["quantise kernel: first CTA starts / last CTA ends"] = [round((qs - float(t0)) / 1e3, 2), round((qe - float(t0)) / 1e3, 2)]
     for name, col in STAMPS:
         out[name] = _mmm(rel(col))
     for name, col in WAITS:
@@ -101,8 +104,11 @@ def main():
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="library option (test hooks included)")
     ap.add_argument("--label", default="")
     ap.add_argument("--raw", default="", help="also save every rank's raw [CTAs, slots] array to this .npz")
+    ap.add_argument("--sweep", default="", metavar="KEY=V1,V2,...",
+                    help="no timeline: time the step (20 launches, slowest rank per launch) under every value of one "
+                         "option, in one process; works with the product build too")
     args = ap.parse_args()
-    if not capi.TRACE:
+    if not capi.TRACE and not args.sweep:
         raise SystemExit("set CATCCOS_B200_TRACE=1: the timeline needs the trace build of the library")
 
     rank = int(os.environ.get("RANK", "0"))
@@ -151,6 +157,28 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3
 
+    if args.sweep:
+        key, values = args.sweep.split("=", 1)
+        res = {}
+        for val in values.split(","):
+            capi.set_option(key, int(val))
+            for _ in range(args.warmup):
+                one()
+            t = torch.tensor([one() for _ in range(20)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts = sorted(t.cpu().tolist())
+            code, st = capi.last_status()
+            res[f"{key}={val}"] = {"p50_us": round(ts[10], 2), "min_us": round(ts[0], 2), "max_us": round(ts[-1], 2), "status": code}
+            progress(f"{key}={val}: {res[f'{key}={val}']}")
+        if rank == 0:
+            print(json.dumps({"sweep": res, "world": world, "shape": [args.m, args.k, args.n], "trace_build": capi.TRACE}))
+        if world > 1:
+            dist.barrier()
+        capi.finalize()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     for i in range(args.warmup):
         us = one()
         if i == 0:

@@ -86,7 +86,7 @@ def main():
         bc, bs = mx_oracle.quantize_weight(workloads.weight_bits(cfg, rank, seed=0))
         b_d, bs_d = torch.from_numpy(bc).cuda(), torch.from_numpy(bs).cuda()
         b_deq = mx_oracle.dequant_weight(bc, bs)
-        for rnd, fuse_mode in enumerate((-1, 0, 5, 4)):  # the default, then every multi-rank variant by name
+        for rnd, fuse_mode in enumerate((-1, 0, 5, 4, 6, 7)):  # the default, then every multi-rank variant by name
             capi.set_option("fuse_mode", fuse_mode)
             bits = [workloads.activation_bits(cfg, r, seed=rnd) for r in range(world)]
             c = torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda")

@@ -100,7 +100,7 @@ def _agmm_round(capi, torch, call, world):
         assert code == 0, (r, st)
 
 
-@pytest.mark.parametrize("fuse_mode", [0, 5])  # pusher warps of the fused kernel / copy engines
+@pytest.mark.parametrize("fuse_mode", [0, 5, 6, 7])  # pusher warps of the fused kernel / copy engines / quantise kernel stores to all
 @pytest.mark.parametrize("cta_pair", [2, 1])
 @pytest.mark.parametrize("world,m,k,n", [(2, 256, 1024, 1024), (4, 128, 512, 256), (8, 16, 1024, 512), (2, 100, 256, 272),
                                          (2, 16, 7168, 512), (4, 48, 4096, 272)])  # the last two: K split in 8 and 4 parts
