@@ -122,7 +122,7 @@ struct TileCoord {
 // Tile visiting order.  n runs fastest so that concurrently running CTAs share one A panel in L2.
 // With gating, m tiles follow arrival: this rank's own shard first, then for each 128-row slice of
 // a shard, the peers in ring order starting after this rank.
-__device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
+__host__ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
 {
     uint32_t mo = idx / n_tiles;
     TileCoord t;

@@ -48,7 +48,7 @@ struct PairSmem {
 };
 
 // Tile order for pairs: as tile_coord, with 256-row tiles.
-__device__ __forceinline__ TileCoord pair_tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
+__host__ __device__ __forceinline__ TileCoord pair_tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
 {
     uint32_t mo = idx / n_tiles;
     TileCoord t;

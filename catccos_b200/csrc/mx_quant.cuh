@@ -146,7 +146,7 @@ __device__ __forceinline__ void quant_group_sync(uint32_t bar_id)
 // follow the quantiser; groups follow one another, so a consumer with several waves of tiles gets complete
 // rows for its first wave while the rest is still on its way.  group_chunks >= chunks: one group.
 // `order` (n entries, n == segs, or n == 0 for the natural order) maps the position in that walk to the segment.
-__device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint32_t segs, uint32_t group_chunks,
+__host__ __device__ __forceinline__ void item_coord(uint32_t item, uint32_t chunks, uint32_t segs, uint32_t group_chunks,
                                            const uint8_t* order, uint32_t order_n, uint32_t& chunk, uint32_t& seg)
 {
     const uint32_t gc = group_chunks == 0u || group_chunks > chunks ? chunks : group_chunks;

@@ -4,10 +4,28 @@
 #include <cstdio>
 #include <sstream>
 
-#include "../../dgemm/device/device_dgemm.hpp"
+#include <climits>
+
+#include "ascend950_fp8_mx_allgather_matmul_device.h"
 #include "ascend950_fp8_mx_allgather_matmul_host.h"
 
-using DeviceOp = Catccos::DGemm::Device::MxAllGatherMatmulDevice;
+using namespace Catccos;
+
+using LayoutA = Catlass::layout::RowMajor;
+using LayoutB = Catlass::layout::RowMajor;
+using LayoutMxScaleA = Catlass::layout::RowMajor;
+using LayoutMxScaleB = Catlass::layout::RowMajor;
+using LayoutC = Catlass::layout::RowMajor;
+
+using ElementA = float8_e4m3_t;
+using ElementB = float8_e4m3_t;
+using ElementMxScaleA = float8_e8m0_t;
+using ElementMxScaleB = float8_e8m0_t;
+using ElementC = bfloat16_t;  // the reference's driver writes half (main.cpp:28); the benchmark's C is bf16
+
+using Config = Ascend950Fp8MxAllGatherMatmulConfig_M0_128<ElementA, LayoutA, ElementB, LayoutB, ElementMxScaleA, LayoutMxScaleA,
+                                                         ElementMxScaleB, LayoutMxScaleB, ElementC, LayoutC>;
+using DeviceOp = Config::Device;
 
 int main(int argc, char** argv)
 {
@@ -74,22 +92,30 @@ int main(int argc, char** argv)
     op->AllocateDeviceSpace(params, tiling, rankId, dataPath);
     uint8_t* symm = static_cast<uint8_t*>(shmem_calloc(1, op->GetSymmetricSize(tiling)));
 
-    DeviceOp::Arguments args{};
-    args.problemShape = {m, n, k};
-    args.rankIdx = static_cast<uint32_t>(rankId);
-    args.rankSize = static_cast<uint32_t>(rankSize);
-    args.commInterval = tiling.commInterval;
-    args.ptrA = params.ptrA;
-    args.ptrB = params.ptrB;
-    args.ptrMxScaleA = params.customPtrs[0];
-    args.ptrMxScaleB = params.customPtrs[1];
-    args.ptrC = params.ptrC;
-    args.ptrSymmetric = symm;
+    Catlass::GemmCoord problemShape{m, n, k};
+    Catlass::MatrixCoord commCoreSplit{tiling.commDataSplit, tiling.commNpuSplit};
+    Catlass::MatrixCoord commBlockShape{tiling.commBlockM, UINT_MAX / 2};
+    Catlass::MatrixCoord commTileShape{tiling.commTileM / 2, tiling.n0};
+    DeviceOp::Arguments args{problemShape,
+                             static_cast<uint32_t>(rankId),
+                             static_cast<uint32_t>(rankSize),
+                             tiling.commInterval,
+                             params.ptrA,
+                             params.ptrB,
+                             params.customPtrs[0],
+                             params.customPtrs[1],
+                             params.ptrC,
+                             symm,
+                             commCoreSplit,
+                             commBlockShape,
+                             commTileShape};
 
     DeviceOp deviceOp;
     int rc = 0;
-    if (deviceOp.Initialize(args) != Catccos::DGemm::Device::Status::kSuccess ||
-        deviceOp.Run(stream) != Catccos::DGemm::Device::Status::kSuccess) {
+    const uint32_t blockNum = 1;  // accepted and ignored: the kernels size their own grids
+    const uint64_t fftsAddr = 0;
+    if (deviceOp.Initialize(args) != Catlass::Status::kSuccess ||
+        deviceOp.Run(stream, blockNum, fftsAddr) != Catlass::Status::kSuccess) {
         ERROR_LOG("device op failed");
         rc = -1;
     }

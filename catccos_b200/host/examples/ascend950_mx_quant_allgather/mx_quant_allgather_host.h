@@ -41,8 +41,15 @@ public:
         const Sizes sz = BufferSizes(cocTiling);
         uint8_t *input = nullptr, *codes = nullptr, *scales = nullptr;
         CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&input), sz.input));
-        CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&codes), sz.codes));
-        CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&scales), sz.scales));
+        // The gathered outputs live in symmetric memory (every rank makes these two calls in the same order):
+        // the peers' shards are then written into them directly instead of passing through a stage and one more
+        // local copy.  FreeDeviceSpace knows both kinds of buffer.
+        void *codesSymm = nullptr, *scalesSymm = nullptr;
+        if (catccos_b200_symm_alloc(sz.codes, &codesSymm) != 0 || catccos_b200_symm_alloc(sz.scales, &scalesSymm) != 0) {
+            ERROR_LOG("MxQuantAllGather: symmetric allocation of the outputs failed");
+        }
+        codes = static_cast<uint8_t*>(codesSymm);
+        scales = static_cast<uint8_t*>(scalesSymm);
         std::vector<uint16_t> host(sz.input / sizeof(uint16_t));
         if (!dataFile.empty()) {
             ReadFileOrThrow(dataFile + "/rank_" + std::to_string(rankId) + "_input.bin", host.data(), sz.input);

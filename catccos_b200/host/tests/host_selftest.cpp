@@ -2,6 +2,7 @@
 // size arithmetic and error behaviour, the launcher table, file helpers.  Exit code 0 = pass.
 #include <cstdio>
 
+#include "../examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_device.h"
 #include "../examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_host.h"
 #include "../examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h"
 #include "dynamic_tiling/launch_map.h"
@@ -14,8 +15,43 @@
         }                                                                \
     } while (0)
 
+// The reference driver's type lines (examples/ascend950_fp8_mx_allgather_matmul/main.cpp:16-31) with half output:
+// they must keep compiling against this tree's headers.
+namespace compat {
+using Config = Ascend950Fp8MxAllGatherMatmulConfig_M0_128<float8_e4m3_t, Catlass::layout::RowMajor, float8_e4m3_t,
+                                                         Catlass::layout::RowMajor, float8_e8m0_t, Catlass::layout::RowMajor,
+                                                         float8_e8m0_t, Catlass::layout::RowMajor, half,
+                                                         Catlass::layout::RowMajor>;
+using DeviceOp = Config::Device;
+}  // namespace compat
+
+static int device_op_checks()
+{
+    // the reference's call sequence (main.cpp:150-183) on a shape the kernels cannot take: it must be refused
+    // by Initialize / Run through Catlass::Status, without touching a GPU
+    Catlass::GemmCoord problemShape{256, 1000, 100};
+    Catlass::MatrixCoord commCoreSplit{16, 2};
+    Catlass::MatrixCoord commBlockShape{64, 0x7FFFFFFFu};
+    Catlass::MatrixCoord commTileShape{32, 256};
+    uint8_t dummy = 0;
+    compat::DeviceOp::Arguments args{problemShape, 0u, 1u, 3u, &dummy, &dummy, &dummy, &dummy, &dummy, &dummy,
+                                     commCoreSplit, commBlockShape, commTileShape};
+    compat::DeviceOp deviceOp;
+    EXPECT(compat::DeviceOp::GetWorkspaceSize(args) == 0);
+    EXPECT(deviceOp.Initialize(args) == Catlass::Status::kErrorInvalidProblem);  // k % 128 != 0
+    EXPECT(deviceOp.Run(nullptr, 1, 0) == Catlass::Status::kErrorInvalidProblem);
+    EXPECT(deviceOp.params().tiling.m == 256 && deviceOp.params().tiling.rankSize == 1);
+    args.problemShape = Catlass::GemmCoord{256, 1024, 512};
+    EXPECT(deviceOp.Initialize(args) == Catlass::Status::kSuccess);
+    EXPECT((std::is_same<compat::DeviceOp::Kernel::ElementC, half>::value));
+    return 0;
+}
+
 int main()
 {
+    if (device_op_checks() != 0) {
+        return 1;
+    }
     auto& reg = OperatorRegistry::Instance();
     auto q = reg.CreateOperator("MxQuantAllGather");
     auto g = reg.CreateOperator("Ascend950Fp8MxAllGatherMatmul");

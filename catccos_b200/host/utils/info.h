@@ -12,6 +12,7 @@
 #include <map>
 #include <string>
 
+#include "../../../include/catccos_b200.h"
 #include "utils.h"
 
 constexpr uint32_t M0 = 128;
@@ -123,19 +124,23 @@ private:
     }
 };
 
+// A buffer an operator allocated: from the symmetric heap (outputs the peers write into) or from cudaMalloc.
+inline void FreeDeviceBuffer(uint8_t* p)
+{
+    if (p != nullptr && catccos_b200_symm_free(p) != 0) {
+        CUDA_CHECK(cudaFree(p));
+    }
+}
+
 inline void FreeDeviceSpace(KernelParams& params)
 {
     uint8_t** main3[] = {&params.ptrA, &params.ptrB, &params.ptrC};
     for (uint8_t** p : main3) {
-        if (*p != nullptr) {
-            CUDA_CHECK(cudaFree(*p));
-            *p = nullptr;
-        }
+        FreeDeviceBuffer(*p);
+        *p = nullptr;
     }
     for (uint32_t i = 0; i < params.customCount; ++i) {
-        if (params.customPtrs[i] != nullptr) {
-            CUDA_CHECK(cudaFree(params.customPtrs[i]));
-        }
+        FreeDeviceBuffer(params.customPtrs[i]);
     }
 }
 

@@ -73,3 +73,14 @@ def test_reference_arm_other_ranks_do_no_work():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
                         "--steps", "1", "--warmup", "1"], capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_tile_and_item_visiting_order(tmp_path):
+    """The order in which CTAs visit output tiles (own shard, then the peers in ring order, slice by slice) and
+    in which quantise / pusher workers visit (chunk, K segment) items, checked on the host against its contract
+    (tests/host/schedule_selftest.cu; compiled with nvcc, runs without a GPU)."""
+    out = tmp_path / "schedule_selftest"
+    subprocess.check_call(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(out),
+                           os.path.join(ROOT, "tests", "host", "schedule_selftest.cu")])
+    r = subprocess.run([str(out)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr
