@@ -29,6 +29,10 @@ EXPORTS = [
     "catccos_b200_mx_quant",
     "catccos_b200_mx_quant_fp4",
     "catccos_b200_mx_gemm",
+    "catccos_b200_mx_gemm_quant_out",
+    "catccos_b200_packed_row_bytes",
+    "catccos_b200_mx_quant_scatter_packed",
+    "catccos_b200_mxfp8_matmul_reduce_scatter",
     "catccos_b200_mx_quant_matmul_static",
     "catccos_b200_mx_quant_matmul_static_status",
     "catccos_b200_last_status",
@@ -84,6 +88,11 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_mx_quant.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_quant_fp4.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_gemm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
+    L.catccos_b200_mx_gemm_quant_out.argtypes = [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]
+    L.catccos_b200_packed_row_bytes.argtypes = [u32]
+    L.catccos_b200_packed_row_bytes.restype = sz
+    L.catccos_b200_mx_quant_scatter_packed.argtypes = [vp, vp, vp, vp, u32, u32, u32]
+    L.catccos_b200_mxfp8_matmul_reduce_scatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant_matmul_static.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32]
     L.catccos_b200_last_status.argtypes = [ctypes.POINTER(u32)]
     L.catccos_b200_mx_quant_matmul_static_status.argtypes = [ctypes.POINTER(u32)]
@@ -91,7 +100,7 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_launch_count.argtypes = []
     L.catccos_b200_launch_count.restype = ctypes.c_uint64
     for name in EXPORTS:
-        if name not in ("catccos_b200_symm_bytes_needed", "catccos_b200_launch_count"):
+        if name not in ("catccos_b200_symm_bytes_needed", "catccos_b200_launch_count", "catccos_b200_packed_row_bytes"):
             getattr(L, name).restype = i32
     if TRACE:
         L.catccos_b200_trace_arm.argtypes = []
@@ -167,8 +176,9 @@ def symm_free(ptr: int) -> None:
     _check("catccos_b200_symm_free", load().catccos_b200_symm_free(ptr))
 
 
-def symm_bytes_needed(t: Tiling, quant_op: bool) -> int:
-    return int(load().catccos_b200_symm_bytes_needed(ctypes.byref(t), 1 if quant_op else 0))
+def symm_bytes_needed(t: Tiling, quant_op) -> int:
+    """quant_op: False / 0 = AllGather-Matmul, True / 1 = quantise + AllGather, 2 = Matmul + ReduceScatter."""
+    return int(load().catccos_b200_symm_bytes_needed(ctypes.byref(t), int(quant_op)))
 
 
 def set_option(key: str, value: int) -> None:
@@ -249,6 +259,42 @@ def mx_gemm(a_codes, a_scales, b, b_scales, out=None, out_dtype=None):
            load().catccos_b200_mx_gemm(_stream(), a_codes.data_ptr(), a_scales.data_ptr(), b.data_ptr(),
                                        b_scales.data_ptr(), out.data_ptr(), m, n, k))
     return out
+
+
+def mx_gemm_quant_out(a_codes, a_scales, b, b_scales):
+    """The GEMM whose epilogue MX-quantises its output: (codes uint8 [M, N], scales uint8 [M, N/32])."""
+    import torch
+
+    m, k = a_codes.shape
+    n = b_scales.shape[1]
+    codes = torch.empty((m, n), dtype=torch.uint8, device=a_codes.device)
+    scales = torch.empty((m, n // 32), dtype=torch.uint8, device=a_codes.device)
+    _check("catccos_b200_mx_gemm_quant_out",
+           load().catccos_b200_mx_gemm_quant_out(_stream(), a_codes.data_ptr(), a_scales.data_ptr(), b.data_ptr(),
+                                                 b_scales.data_ptr(), codes.data_ptr(), scales.data_ptr(), m, n, k))
+    return codes, scales
+
+
+def packed_row_bytes(n: int) -> int:
+    return int(load().catccos_b200_packed_row_bytes(n))
+
+
+def mx_quant_scatter_packed(x_bf16, expanded_row_idx, packed_out, top_k: int) -> None:
+    """Quantises every token (row of x) once and writes its packed row to each of its top_k destination rows."""
+    tokens, n = x_bf16.shape
+    _check("catccos_b200_mx_quant_scatter_packed",
+           load().catccos_b200_mx_quant_scatter_packed(_stream(), x_bf16.data_ptr(), expanded_row_idx.data_ptr(),
+                                                       packed_out.data_ptr(), tokens, n, top_k))
+
+
+def mxfp8_matmul_reduce_scatter(a_codes, a_scales, b, b_scales, d, symm: int, world: int) -> None:
+    """d [m / world, n] = this rank's row chunk of the sum over ranks of dequant(a) x dequant(b); m is the whole M."""
+    m, k = a_codes.shape
+    n = b_scales.shape[1]
+    t = make_tiling(m, k, n, world)
+    _check("catccos_b200_mxfp8_matmul_reduce_scatter",
+           load().catccos_b200_mxfp8_matmul_reduce_scatter(_stream(), a_codes.data_ptr(), b.data_ptr(), a_scales.data_ptr(),
+                                                           b_scales.data_ptr(), d.data_ptr(), symm, ctypes.byref(t), 0))
 
 
 def mx_quant_matmul_static(a_bf16, b, b_scales, c) -> None:

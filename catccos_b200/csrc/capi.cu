@@ -110,6 +110,8 @@ struct RankCtx {
     StatusBlock* status = nullptr;  // device memory
     // split-K scratch of this rank's GEMM launches: one fp32 partial tile and four flag words per SM, and the
     // count of split launches so far (the flags are epochs).  Launches of one rank are stream-ordered.
+    uint8_t* fp4_bt = nullptr;  // the transposed copy of a packed E2M1 weight, made on every call that gets one
+    size_t fp4_bt_bytes = 0;
     float* splitk_ws = nullptr;
     uint32_t* splitk_flags = nullptr;
     uint32_t splitk_epoch = 0;
@@ -180,6 +182,8 @@ int setup_rank_ctx(RankCtx& rc, int device)
     CUDA_TRY(cudaDeviceGetAttribute(&rc.num_sms, cudaDevAttrMultiProcessorCount, device));
     CUDA_TRY(cudaMalloc(&rc.status, sizeof(StatusBlock)));
     CUDA_TRY(cudaMemset(rc.status, 0, sizeof(StatusBlock)));
+    CUDA_TRY(cudaMalloc(&rc.fp4_bt, 1u << 20));
+    rc.fp4_bt_bytes = 1u << 20;
     CUDA_TRY(cudaMalloc(&rc.splitk_ws, (size_t)rc.num_sms * kSplitKTileBytes));
     CUDA_TRY(cudaMalloc(&rc.splitk_flags, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
     CUDA_TRY(cudaMemset(rc.splitk_flags, 0, (size_t)rc.num_sms * 4 * sizeof(uint32_t)));
@@ -207,6 +211,7 @@ void destroy_rank_ctx(RankCtx& rc)
 {
     cudaSetDevice(rc.device);
     if (rc.status) cudaFree(rc.status);
+    if (rc.fp4_bt) cudaFree(rc.fp4_bt);
     if (rc.splitk_ws) cudaFree(rc.splitk_ws);
     if (rc.splitk_flags) cudaFree(rc.splitk_flags);
     if (rc.side) cudaStreamDestroy(rc.side);
@@ -397,14 +402,67 @@ int launch_quant_push_ordered(RankCtx& rc, cudaStream_t st, QuantPushParams& p, 
     return 0;
 }
 
+// Tensor maps depend on (address, extents, box) only; a decode loop calls with the same few buffers over and
+// over, and an encode costs about as much as the launch it precedes.  A small most-recently-used table keeps the
+// last maps (calls of one process are serialised by its callers: one host thread per rank).
+struct MapKey {
+    const void* base;
+    uint64_t inner, outer;
+    uint32_t box_inner, box_outer;
+    bool fp4;
+    bool operator==(const MapKey& o) const
+    {
+        return base == o.base && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
+               box_outer == o.box_outer && fp4 == o.fp4;
+    }
+};
+constexpr int kMapCacheSize = 16;
+struct MapCache {
+    MapKey key[kMapCacheSize] = {};
+    CUtensorMap map[kMapCacheSize];
+    uint64_t used[kMapCacheSize] = {};
+    uint64_t clock = 0;
+} g_maps;
+
+int encode_map_2d_uncached(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                           uint32_t box_outer, bool fp4);
+
+// inner / outer / box in elements; fp4: two E2M1 values per byte in global memory
 int encode_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                  uint32_t box_outer)
+                  uint32_t box_outer, bool fp4 = false)
+{
+    const MapKey k{base, inner, outer, box_inner, box_outer, fp4};
+    int victim = 0;
+    for (int i = 0; i < kMapCacheSize; ++i) {
+        if (g_maps.used[i] != 0 && g_maps.key[i] == k) {
+            g_maps.used[i] = ++g_maps.clock;
+            *map = g_maps.map[i];
+            return 0;
+        }
+        if (g_maps.used[i] < g_maps.used[victim]) {
+            victim = i;
+        }
+    }
+    int rc = encode_map_2d_uncached(map, base, inner, outer, box_inner, box_outer, fp4);
+    if (rc == 0) {
+        g_maps.key[victim] = k;
+        g_maps.map[victim] = *map;
+        g_maps.used[victim] = ++g_maps.clock;
+    }
+    return rc;
+}
+
+int encode_map_2d_uncached(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                           uint32_t box_outer, bool fp4)
 {
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner};  // bytes (8-bit elements)
+    cuuint64_t strides[1] = {fp4 ? inner / 2 : inner};  // bytes: 8-bit elements, or 4-bit ones packed in pairs
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CU_TRY(g.drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+    // packed 4-bit values land in shared memory sixteen to a 16-byte chunk (8 bytes of values, 8 bytes of gap):
+    // the same 128 bytes per 128 values as the 8-bit types, so boxes, swizzle and descriptors stay as they are
+    const CUtensorMapDataType dt = fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CU_TRY(g.drv.TensorMapEncodeTiled(map, dt, 2, const_cast<void*>(base), dims, strides, box,
                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
     return 0;
@@ -500,7 +558,7 @@ struct GemmPlan {
 };
 
 // Tiling of one GEMM launch: CTA pairs or single CTAs, tile width, and the number of K parts.
-GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
+GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K, bool no_split = false)
 {
     // waves x K-tile period of each candidate (same K for all, so K drops out)
     const uint32_t m128 = (Mg + 127) / 128, m256 = (Mg + 255) / 256;
@@ -517,7 +575,7 @@ GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
     // Split K when the tiles would leave at least half of the SMs idle: every (tile, K part) pair gets its
     // own CTA, the parts' partial tiles meet in this rank's scratch.  Needs the scratch (the allocation-free
     // entry point has none), an even split and at least four K tiles per part.
-    if (rc.splitk_ws != nullptr && g.split_k != 1 && g.cta_pair != 1) {
+    if (rc.splitk_ws != nullptr && g.split_k != 1 && g.cta_pair != 1 && !no_split) {
         const uint32_t sbn = (bn == 128 || N <= 128) ? 128u : 256u;
         const uint32_t stiles = m128 * (sbn == 128 ? n128 : n256);
         const uint32_t k_tiles = K / kGemmBlockK;
@@ -545,9 +603,15 @@ GemmPlan plan_gemm(const RankCtx& rc, uint32_t Mg, uint32_t N, uint32_t K)
 
 // overlap_predecessor: the kernel launched just before on `st` is this library's quantise kernel, whose output
 // the GEMM reads only behind grid_dep_wait(); the GEMM may then be scheduled while that kernel drains.
+// epilogue: what the epilogue warps do with a finished tile (never combined with the quantise warps inside)
+enum Epilogue { kEpiStore = 0,    // round to bf16 / fp16 and store C
+                kEpiMxQuant = 1,  // MX-quantise the output (p.c = codes, p.c_scales)
+                kEpiScatter = 2 };  // Matmul + ReduceScatter: fp32 partial rows to the stage of the rank that owns them
+
 int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, GemmParams& p, bool fused_quant = false,
-                bool overlap_predecessor = false)
+                bool overlap_predecessor = false, Epilogue epilogue = kEpiStore)
 {
+    const bool mx_out = epilogue == kEpiMxQuant, scatter = epilogue == kEpiScatter;
     if (!g.drv.Load()) {
         return CATCCOS_B200_ECUDA;
     }
@@ -555,7 +619,7 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         ERROR_LOG("mx gemm needs K %% 128 == 0 and N %% 16 == 0 (got M=%u N=%u K=%u)", p.Mg, p.N, p.K);
         return CATCCOS_B200_EINVAL;
     }
-    if ((((uintptr_t)a | (uintptr_t)b) & 15u) || ((uintptr_t)p.c & 31u) || ((uintptr_t)p.a_scales & 3u) ||
+    if ((((uintptr_t)a | (uintptr_t)b) & 15u) || (!scatter && ((uintptr_t)p.c & 31u)) || ((uintptr_t)p.a_scales & 3u) ||
         ((uintptr_t)p.b_scales & 1u)) {
         ERROR_LOG("mx gemm operands must be 16-byte aligned (the output 32-byte aligned)");
         return CATCCOS_B200_EINVAL;
@@ -571,23 +635,59 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
         p.trace = p.q.trace = p.push.trace = rc.trace;
     }
 #endif
-    p.a_e5m2 = g.a_dtype == 1 ? 1u : 0u;
-    p.b_e5m2 = g.b_dtype == 1 ? 1u : 0u;
-    const GemmPlan plan = plan_gemm(rc, p.Mg, p.N, p.K);
+    p.a_fmt = g.a_dtype == 2 ? 5u : (g.a_dtype == 1 ? 1u : 0u);
+    p.b_fmt = g.b_dtype == 2 ? 5u : (g.b_dtype == 1 ? 1u : 0u);
+    const bool a_fp4 = g.a_dtype == 2, b_fp4 = g.b_dtype == 2;
+    if ((a_fp4 && (((uintptr_t)a & 31u) || p.K % 128 != 0)) || (b_fp4 && (((uintptr_t)b & 31u) || p.N % 128 != 0))) {
+        ERROR_LOG("mx gemm: packed E2M1 operands must be 32-byte aligned, with K (and N for B) a multiple of 128");
+        return CATCCOS_B200_EINVAL;
+    }
+    if (b_fp4) {
+        // the tensor core takes 4-bit operands K-major only: transpose the weight [K, N/2] -> [N, K/2] into this
+        // rank's scratch (grown on first use; a few microseconds for a weight of some megabytes)
+        const size_t need = (size_t)p.N * (p.K / 2);
+        if (rc.fp4_bt == nullptr) {
+            return CATCCOS_B200_ESTATE;  // the allocation-free entry point has no scratch for it
+        }
+        if (need > rc.fp4_bt_bytes) {
+            CUDA_TRY(cudaStreamSynchronize(st));
+            CUDA_TRY(cudaFree(rc.fp4_bt));
+            CUDA_TRY(cudaMalloc(&rc.fp4_bt, need));
+            rc.fp4_bt_bytes = need;
+        }
+        dim3 tg((p.N + 63) / 64, (p.K + 63) / 64);
+        fp4_transpose_kernel<<<tg, 256, 0, st>>>(static_cast<const uint8_t*>(b), rc.fp4_bt, p.K, p.N);
+        g_launches++;
+        CUDA_TRY(cudaGetLastError());
+        b = rc.fp4_bt;
+        p.b_kmajor = 1;
+        overlap_predecessor = false;
+    }
+    GemmPlan plan = plan_gemm(rc, p.Mg, p.N, p.K);
+    if (scatter && plan.ksplit > 1) {
+        plan = plan_gemm(rc, p.Mg, p.N, p.K, true);  // the owner adds whole tiles: K stays in one piece
+    }
     const bool use_pair = plan.use_pair;
     const uint32_t bn = plan.block_n, ksplit = plan.ksplit;
     const uint32_t m256 = (p.Mg + 255) / 256, n256 = (p.N + 255) / 256;
     const uint32_t max_pairs = (uint32_t)rc.num_sms / 2;
     if (use_pair) {
         CUtensorMap pa, pb;
-        int rc2 = encode_map_2d(&pa, a, p.K, p.Mg, kGemmBlockK, 128);
+        int rc2 = encode_map_2d(&pa, a, p.K, p.Mg, kGemmBlockK, 128, a_fp4);
         if (rc2 != 0) return rc2;
-        rc2 = encode_map_2d(&pb, b, p.N, p.K, 128, kGemmBlockK);
+        rc2 = b_fp4 ? encode_map_2d(&pb, b, p.K, p.N, kGemmBlockK, 128, true)
+                    : encode_map_2d(&pb, b, p.N, p.K, 128, kGemmBlockK, false);
         if (rc2 != 0) return rc2;
         const uint32_t tiles = m256 * n256;
 #ifdef CATCCOS_TRACE
         rc.trace_grid = (int)(2 * std::min(tiles, max_pairs));
 #endif
+        if (mx_out) {
+            return launch_gemm_pair_inst<MxOut, false>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
+        }
+        if (scatter) {
+            return launch_gemm_pair_inst<ScatterOut, false>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
+        }
         if (fused_quant) {
             return f16 ? launch_gemm_pair_inst<__half, true>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor)
                        : launch_gemm_pair_inst<__nv_bfloat16, true>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
@@ -596,9 +696,9 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
                    : launch_gemm_pair_inst<__nv_bfloat16, false>((int)max_pairs, tiles, st, pa, pb, p, overlap_predecessor);
     }
     CUtensorMap ta, tb;
-    int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM);
+    int rcode = encode_map_2d(&ta, a, p.K, p.Mg, kGemmBlockK, kGemmBlockM, a_fp4);
     if (rcode != 0) return rcode;
-    rcode = encode_map_2d(&tb, b, p.N, p.K, 128, kGemmBlockK);
+    rcode = b_fp4 ? encode_map_2d(&tb, b, p.K, p.N, kGemmBlockK, bn, true) : encode_map_2d(&tb, b, p.N, p.K, 128, kGemmBlockK, false);
     if (rcode != 0) return rcode;
     const uint32_t tiles = ((p.Mg + kGemmBlockM - 1) / kGemmBlockM) * ((p.N + bn - 1) / bn);
     int grid = (int)(tiles < (uint32_t)rc.num_sms ? tiles : (uint32_t)rc.num_sms);
@@ -614,6 +714,12 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
 #endif
 #define CATCCOS_GEMM_CASE(BN)                                                                         \
     if (bn == BN) {                                                                                   \
+        if (mx_out) {                                                                                 \
+            return launch_gemm_inst<BN, MxOut, false>(grid, st, ta, tb, p, overlap_predecessor);      \
+        }                                                                                             \
+        if (scatter) {                                                                                \
+            return launch_gemm_inst<BN, ScatterOut, false>(grid, st, ta, tb, p, overlap_predecessor); \
+        }                                                                                             \
         if (fused_quant) {                                                                            \
             return f16 ? launch_gemm_inst<BN, __half, true>(grid, st, ta, tb, p, overlap_predecessor)         \
                        : launch_gemm_inst<BN, __nv_bfloat16, true>(grid, st, ta, tb, p, overlap_predecessor); \
@@ -1193,6 +1299,9 @@ size_t catccos_b200_symm_bytes_needed(const catccos_b200_tiling_t* t, int quant_
     if (t == nullptr) return 0;
     const size_t W = t->rankSize ? t->rankSize : 1;
     const size_t M = t->m;
+    if (quant_op == 2) {  // Matmul + ReduceScatter: two stages of the whole fp32 product (m is the whole M there)
+        return kHeaderBytes + 2 * align_up(M * (size_t)t->n * sizeof(float), 1024) + 2048;
+    }
     const size_t K = quant_op ? t->n : t->k;
     return kHeaderBytes + 2 * (align_up(W * M * K, 1024) + align_up(W * M * (K / 32), 1024)) + 2048;
 }
@@ -1335,8 +1444,9 @@ int catccos_b200_mx_quant_allgather(void* stream, const void* in_bf16, void* out
             ds[d] = (direct ? ss->base[d] + off_s : base + L.scales_off) + (size_t)rank * M * (K / 32);
             df[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
         }
-        // nobody consumes this operator's rows early: four large slices per peer keep the copies long
-        const uint32_t slice_rows = std::max(kCopySliceRows, (uint32_t)align_up((M + 3) / 4, kCopySliceRows));
+        // nobody consumes this operator's rows early: one slice per peer (three copies: scales, codes, flags)
+        // keeps the copies long and their fixed start-up cost small
+        const uint32_t slice_rows = (uint32_t)align_up(M, kRowsPerChunk);
         rcode = copy_engine_push(rc, st, W, rank, M, K, q.segs_per_chunk, slice_rows, q.dst_codes[rank], q.dst_scales[rank],
                                  q.dst_flags[rank], dc, ds, df);
         if (rcode != 0) return rcode;
@@ -1400,6 +1510,163 @@ int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const
     return launch_gemm(rc, (cudaStream_t)stream, a, b, p);
 }
 
+int catccos_b200_mx_gemm_quant_out(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                   void* c_codes, void* c_scales, uint32_t m, uint32_t n, uint32_t k)
+{
+    if (!a || !a_scale || !b || !b_scale || !c_codes || !c_scales) {
+        return CATCCOS_B200_EINVAL;
+    }
+    if (n % 32 != 0) {
+        ERROR_LOG("mx gemm with quantised output: n must be a multiple of 32 (got %u)", n);
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    RankCtx& rc = cur();
+    GemmParams p = {};
+    p.a_scales = (const uint8_t*)a_scale;
+    p.b_scales = (const uint8_t*)b_scale;
+    p.c = c_codes;
+    p.c_scales = (uint8_t*)c_scales;
+    p.c_tiny_rule = g.tiny_block_rule != 0 ? kQuantDeviceTiny : kQuantGolden;
+    p.Mg = m;
+    p.N = n;
+    p.K = k;
+    p.flags = nullptr;
+    p.world = 1;
+    p.m_local = m;
+    return launch_gemm(rc, (cudaStream_t)stream, a, b, p, false, false, kEpiMxQuant);
+}
+
+// Matmul + ReduceScatter: what plan_gemm will choose for the N tile (the reducer walks the same tiles)
+static uint32_t scatter_block_n(const RankCtx& rc, uint32_t M, uint32_t N, uint32_t K)
+{
+    GemmPlan plan = plan_gemm(rc, M, N, K);
+    if (plan.ksplit > 1) {
+        plan = plan_gemm(rc, M, N, K, true);
+    }
+    return plan.use_pair ? kPairBlockN : plan.block_n;
+}
+
+int catccos_b200_mxfp8_matmul_reduce_scatter(void* stream, const void* a, const void* b, const void* a_scale,
+                                             const void* b_scale, void* d, void* symm, const catccos_b200_tiling_t* t,
+                                             uint32_t magic)
+{
+    (void)magic;
+    if (!t || !a || !b || !a_scale || !b_scale || !d) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    const uint32_t M = t->m, K = t->k, N = t->n, W = t->rankSize;  // m is the whole M: every rank holds all rows of its K slice
+    if (W != (uint32_t)g.world || M == 0 || K % kGemmBlockK != 0 || N % 16 != 0 || M % W != 0 || (M / W) % 32 != 0) {
+        ERROR_LOG("matmul reduce scatter: rankSize %u (world %d), M=%u K=%u N=%u unsupported (M / rankSize must be a "
+                  "multiple of 32, K of 128, N of 16)", W, g.world, M, K, N);
+        return CATCCOS_B200_EINVAL;
+    }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t rank = (uint32_t)g.rank, rows = M / W;
+    const bool produce = (g.phase_mask & 1) != 0, consume = (g.phase_mask & 2) != 0;
+    if (W == 1) {
+        // nothing to reduce: the plain GEMM writes D
+        GemmParams p = {};
+        p.a_scales = (const uint8_t*)a_scale;
+        p.b_scales = (const uint8_t*)b_scale;
+        p.c = d;
+        p.Mg = M;
+        p.N = N;
+        p.K = K;
+        p.world = 1;
+        p.m_local = M;
+        return launch_gemm(rc, st, a, b, p);
+    }
+    SymmAlloc* sa = find_symm(symm);
+    if (sa == nullptr) {
+        ERROR_LOG("matmul reduce scatter: symm must come from catccos_b200_symm_alloc");
+        return CATCCOS_B200_ENOTSYMM;
+    }
+    const uint32_t bn = scatter_block_n(rc, M, N, K);
+    const uint32_t n_tiles = (N + bn - 1) / bn;
+    const size_t stage_bytes = ((sa->size - kHeaderBytes) / 2) & ~(size_t)1023;
+    const size_t need = (size_t)M * N * sizeof(float);  // world slots of [rows, N] fp32
+    if (sa->size < kHeaderBytes + 2048 || need > stage_bytes || (size_t)(rows / 32) * n_tiles > kMaxFlags) {
+        ERROR_LOG("matmul reduce scatter: symmetric buffer of %zu bytes too small (needs %zu)", sa->size,
+                  kHeaderBytes + 2 * need + 2048);
+        return CATCCOS_B200_ENOMEM;
+    }
+    if (produce) {
+        sa->epoch[g.rank] += 1;
+    }
+    const uint32_t epoch = sa->epoch[g.rank];
+    const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * stage_bytes;
+    if (produce) {
+        GemmParams p = {};
+        p.a_scales = (const uint8_t*)a_scale;
+        p.b_scales = (const uint8_t*)b_scale;
+        p.c = nullptr;
+        p.Mg = M;
+        p.N = N;
+        p.K = K;
+        p.world = W;
+        p.rank = rank;
+        p.m_local = M;
+        p.epoch = epoch;
+        p.rs_rows = rows;
+        for (uint32_t dr = 0; dr < W; ++dr) {
+            p.rs_dst[dr] = reinterpret_cast<float*>(sa->base[dr] + stage_off);
+            p.rs_flags[dr] = reinterpret_cast<uint32_t*>(sa->base[dr] + kFlagsOff) + (size_t)rank * kMaxFlags;
+        }
+        rcode = launch_gemm(rc, st, a, b, p, false, false, kEpiScatter);
+        if (rcode != 0) return rcode;
+    }
+    if (consume) {
+        const uint32_t units = (rows / 32) * n_tiles;
+        const uint32_t grid = std::min(units, (uint32_t)rc.num_sms * 4u);
+        const float* parts = reinterpret_cast<const float*>(sa->base[rank] + stage_off);
+        const uint32_t* flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
+        if (g.c_dtype == 1) {
+            mx_reduce_scatter_kernel<__half><<<grid, 256, 0, st>>>(parts, flags, kMaxFlags, W, rows, N, bn, epoch, (__half*)d,
+                                                                   g.timeout_ns, rc.status);
+        } else {
+            mx_reduce_scatter_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(parts, flags, kMaxFlags, W, rows, N, bn, epoch,
+                                                                          (__nv_bfloat16*)d, g.timeout_ns, rc.status);
+        }
+        g_launches++;
+        CUDA_TRY(cudaGetLastError());
+    }
+    return 0;
+}
+
+size_t catccos_b200_packed_row_bytes(uint32_t n) { return packed_row_bytes(n); }
+
+int catccos_b200_mx_quant_scatter_packed(void* stream, const void* in_bf16, const int32_t* expanded_row_idx, void* packed_out,
+                                         uint32_t tokens, uint32_t n, uint32_t top_k)
+{
+    if (!in_bf16 || !expanded_row_idx || !packed_out || n == 0 || n % 32 != 0 || top_k == 0) {
+        return CATCCOS_B200_EINVAL;
+    }
+    if ((((uintptr_t)in_bf16 | (uintptr_t)packed_out) & 15u) != 0) {
+        return CATCCOS_B200_EINVAL;  // rows are read and written 16 bytes at a time
+    }
+    if (tokens == 0) {
+        return 0;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    RankCtx& rc = cur();
+    const uint32_t per_cta = kQuantThreads / 32;
+    uint32_t grid = (tokens + per_cta - 1) / per_cta;
+    grid = std::min(grid, (uint32_t)rc.num_sms * 6u);
+    mx_quant_scatter_packed_kernel<<<grid, kQuantThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const uint16_t*>(in_bf16), expanded_row_idx, static_cast<uint8_t*>(packed_out), tokens, n, top_k,
+        g.tiny_block_rule != 0 ? 1u : 0u);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
 int catccos_b200_last_status(uint32_t out[4])
 {
     if (out == nullptr || g.mode == Mode::kNone) {
@@ -1431,9 +1698,9 @@ int catccos_b200_set_option(const char* key, int64_t value)
         g.tiny_block_rule = (int)value;
     } else if (k == "c_dtype" && (value == 0 || value == 1)) {
         g.c_dtype = (int)value;
-    } else if (k == "a_dtype" && (value == 0 || value == 1)) {
+    } else if (k == "a_dtype" && value >= 0 && value <= 2) {
         g.a_dtype = (int)value;
-    } else if (k == "b_dtype" && (value == 0 || value == 1)) {
+    } else if (k == "b_dtype" && value >= 0 && value <= 2) {
         g.b_dtype = (int)value;
     } else if (k == "timeout_ms" && value > 0 && value <= 600000) {
         g.timeout_ns = (uint64_t)value * 1000000ull;

@@ -40,6 +40,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "mx_quant.cuh"
 
@@ -57,9 +59,20 @@ constexpr uint32_t kTmemCols = 512;
 struct GemmParams {
     const uint8_t* a_scales;  // [Mg, K/32]
     const uint8_t* b_scales;  // [K/64, N, 2]
-    void* c;                  // [Mg, N]
+    void* c;                  // [Mg, N]: bf16 / fp16, or E4M3 codes when the epilogue quantises (MxOut)
+    uint8_t* c_scales;        // MxOut only: E8M0 [Mg, N/32], one scale per 32 output columns of a row
+    uint32_t c_tiny_rule;     // MxOut only: kQuantGolden / kQuantDeviceTiny
+    // ScatterOut only (Matmul + ReduceScatter): rows [d * rs_rows, (d + 1) * rs_rows) of this rank's fp32 partial
+    // product go to rank d's stage, slot `rank`; one flag word per (32-row block, N tile) says they have landed
+    float* rs_dst[kMaxRanks];       // rank d's partials [world][rs_rows][N] (this rank's own for d == rank)
+    uint32_t* rs_flags[kMaxRanks];  // rank d's flag words for this source: [(rs_rows / 32) * n_tiles]
+    uint32_t rs_rows;
     uint32_t Mg, N, K;
-    uint32_t a_e5m2, b_e5m2;  // element type of the A / B codes: 0 = E4M3, 1 = E5M2
+    uint32_t b_kmajor;        // 1: B is the transposed copy [N, K] (K-major operand); the tensor core takes 4-bit
+                              // operands in that form only, so packed E2M1 weights are transposed once per call
+    uint32_t a_fmt, b_fmt;    // element type of the A / B codes as tcgen05 names it: 0 = E4M3, 1 = E5M2, 5 = E2M1
+                              // (E2M1: packed two per byte in global memory, unpacked by TMA into the
+                              // 16-values-per-16-bytes form kind::mxf8f6f4 reads from shared memory)
     // gating on the quantise-and-push kernel (flags == nullptr: all of A is already in place)
     const uint32_t* flags;  // [world][flag_stride] epoch words in this GPU's symmetric header,
                             // word chunk * segs + seg covers 16 rows x (seg_ktiles * 128) columns of K
@@ -285,6 +298,130 @@ __device__ __forceinline__ void store_c_chunk(OutT* c, const GemmParams& p, uint
     }
 }
 
+// Output "type" of the epilogue that MX-quantises what it has just computed: the 32 consecutive columns a lane
+// holds of one output row are exactly one MX block, so the lane rounds them to bf16 (the 16-bit tile the
+// reference's epilogue quantises from), takes the block's exponent, and writes 32 E4M3 codes and one E8M0 byte.
+// It replaces CommBlockMxQuant::QuantFromUb / QuantFromUb2D
+// (include/catccos/comm/block/comm_block_mx_quant.hpp:209-310): quantising a GEMM output tile before it leaves
+// the core, without materialising the 16-bit tensor.
+struct MxOut {};
+
+template <>
+__device__ __forceinline__ void store_c_chunk<MxOut>(MxOut*, const GemmParams& p, uint32_t row, uint32_t col,
+                                                     const uint32_t (&r)[32])
+{
+    if (row >= p.Mg || col >= p.N) {
+        return;  // N is a multiple of 32 here (checked by the host), so a chunk is inside or outside as a whole
+    }
+    uint32_t w[16];
+    uint32_t amax = 0;
+#pragma unroll
+    for (uint32_t e = 0; e < 16; ++e) {
+        w[e] = pack2<__nv_bfloat16>(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+        const uint32_t a = w[e] & 0x7FFF7FFFu;
+        amax = max(amax, max(a & 0xFFFFu, a >> 16));
+    }
+    uint32_t byte;
+    float mul;
+    bool nonfinite;
+    block_scale(amax, p.c_tiny_rule == kQuantDeviceTiny, 8u, byte, mul, nonfinite);
+    uint32_t o[8];
+#pragma unroll
+    for (uint32_t e = 0; e < 8; ++e) {
+        o[e] = nonfinite ? 0x7F7F7F7Fu : encode4(w[2 * e], w[2 * e + 1], mul, false);
+    }
+    st_global_v8(static_cast<uint8_t*>(p.c) + (size_t)row * p.N + col, o);
+    p.c_scales[(size_t)row * (p.N / 32u) + col / 32u] = (uint8_t)byte;
+}
+
+// Output "type" of the epilogue of Matmul + ReduceScatter: the fp32 accumulator rows go, unrounded, to the stage
+// of the rank that owns them (a peer's over NVLink, or this rank's own), where that rank adds the partial
+// products of all ranks in rank order.  It replaces the compute half of MatmulReduceScatterMxTla
+// (include/catccos/dgemm/kernel/matmul_reduce_scatter_mx_tla.hpp:36-125), whose partial tiles travel through
+// the symmetric workspace as 16-bit values; fp32 partials and a fixed order make the sum independent of timing.
+struct ScatterOut {};
+
+template <>
+__device__ __forceinline__ void store_c_chunk<ScatterOut>(ScatterOut*, const GemmParams& p, uint32_t row, uint32_t col,
+                                                          const uint32_t (&r)[32])
+{
+    if (row >= p.Mg || col >= p.N) {
+        return;
+    }
+    const uint32_t d = row / p.rs_rows;
+    float* dst = p.rs_dst[d] + ((size_t)p.rank * p.rs_rows + (row - d * p.rs_rows)) * p.N + col;
+    if (col + 32u <= p.N) {
+#pragma unroll
+        for (uint32_t v = 0; v < 8; ++v) {
+            reinterpret_cast<float4*>(dst)[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                             __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        }
+    } else {
+        for (uint32_t j = 0; col + j < p.N; ++j) {
+            dst[j] = __uint_as_float(r[j]);
+        }
+    }
+}
+
+// After an epilogue warp has stored its 32 rows of a tile: the rows are fenced and flagged at their owner.
+template <typename OutT>
+__device__ __forceinline__ void publish_tile_rows(const GemmParams& p, uint32_t row0, uint32_t n_tile, uint32_t n_tiles,
+                                                  uint32_t lane)
+{
+    if constexpr (std::is_same<OutT, ScatterOut>::value) {
+        __syncwarp();
+        if (lane == 0 && row0 < p.Mg) {
+            const uint32_t d = row0 / p.rs_rows;
+            const uint32_t block = (row0 - d * p.rs_rows) / 32u;
+            __threadfence_system();
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.rs_flags[d] + (size_t)block * n_tiles + n_tile), "r"(p.epoch)
+                         : "memory");
+        }
+    }
+}
+
+// The consumer half of Matmul + ReduceScatter: this rank's rows of the product, D [rs_rows, N] = the sum over the
+// source ranks, in rank order, of the fp32 partials in this rank's stage.  One CTA per (32-row block, N tile) of
+// the producing GEMM, as soon as all ranks have flagged it (bounded wait).
+template <typename OutT>
+__global__ void __launch_bounds__(256) mx_reduce_scatter_kernel(const float* __restrict__ parts, const uint32_t* flags,
+                                                                uint32_t flag_stride, uint32_t world, uint32_t rs_rows, uint32_t N,
+                                                                uint32_t bn, uint32_t epoch, OutT* __restrict__ d,
+                                                                uint64_t timeout_ns, StatusBlock* status)
+{
+    const uint32_t n_tiles = (N + bn - 1) / bn;
+    const uint32_t units = (rs_rows / 32u) * n_tiles;
+    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const uint32_t rb = unit / n_tiles, nt = unit - rb * n_tiles;
+        if (threadIdx.x < world && !wait_flag_ge(flags + (size_t)threadIdx.x * flag_stride + unit, epoch, timeout_ns, status)) {
+            report_status(status, kStatusFlagTimeout, threadIdx.x, unit, epoch);
+        }
+        __syncthreads();
+        if (status_tripped(status)) {
+            return;  // nothing is written from partials that never arrived
+        }
+        const uint32_t c0 = nt * bn;
+        const uint32_t cols4 = (min(bn, N - c0)) / 4u;
+        for (uint32_t i = threadIdx.x; i < 32u * cols4; i += blockDim.x) {
+            const uint32_t r = i / cols4, c = c0 + (i - r * cols4) * 4u;
+            const size_t row = (size_t)rb * 32u + r;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s = 0; s < world; ++s) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(parts + ((size_t)s * rs_rows + row) * N + c));
+                acc.x += v.x;
+                acc.y += v.y;
+                acc.z += v.z;
+                acc.w += v.w;
+            }
+            uint2 o;
+            o.x = pack2<OutT>(acc.x, acc.y);
+            o.y = pack2<OutT>(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(d + row * N + c) = o;
+        }
+        __syncthreads();
+    }
+}
+
 template <uint32_t BLOCK_N, typename OutT, bool FUSED_QUANT>
 __global__ void __launch_bounds__(FUSED_QUANT ? kGemmFusedThreads : kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p)
@@ -357,6 +494,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t num_units = num_tiles * ksplit;
         uint32_t it = 0, ti = 0;
         bool alive = true;
+        // packed 4-bit operands arrive as half the bytes they occupy in shared memory (the gaps are not written)
+        const uint32_t tx_bytes = (p.a_fmt == 5u ? S::kABytes / 2u : S::kABytes) + (p.b_fmt == 5u ? S::kBBytes / 2u : S::kBBytes);
         for (uint32_t unit = blockIdx.x; alive && unit < num_units; unit += gridDim.x, ++ti) {
             const uint32_t ks = unit / num_tiles;
             TileCoord tc = tile_coord(unit - ks * num_tiles, n_tiles, m_tiles, p);
@@ -390,13 +529,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         CATCCOS_TR_STAMP(p.trace, kTrTileStart + ti);
                     }
                     CATCCOS_TR_STAMP_FIRST(p.trace, kTrProdFirstTma);
-                    mbar_arrive_expect_tx(&full[s], S::kABytes + S::kBBytes);
+                    mbar_arrive_expect_tx(&full[s], tx_bytes);
                     tma_load_2d(smem + S::kOffA + s * S::kABytes, &tmap_a, &full[s], (int32_t)(kt * kGemmBlockK),
                                 (int32_t)m0);
-                    // B is [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
-                    for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
-                        tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full[s],
-                                    (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
+                    if (p.b_kmajor) {
+                        // the transposed copy [N, K]: box = 128 (K, contiguous) x BLOCK_N rows
+                        tma_load_2d(smem + S::kOffB + s * S::kBBytes, &tmap_b, &full[s], (int32_t)(kt * kGemmBlockK),
+                                    (int32_t)n0);
+                    } else {
+                        // B is [K, N] row-major: box = 128 (N, contiguous) x 128 (K); one box per 128 columns
+                        for (uint32_t h = 0; h < BLOCK_N / 128; ++h) {
+                            tma_load_2d(smem + S::kOffB + s * S::kBBytes + h * 16384u, &tmap_b, &full[s],
+                                        (int32_t)(n0 + h * 128u), (int32_t)(kt * kGemmBlockK));
+                        }
                     }
                     CATCCOS_TR_STAMP(p.trace, kTrProdLastTma);
                 }
@@ -409,8 +554,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // else can (the MMAs, and the commit that releases the stage) and nothing more: four MMAs of 128 cycles
         // each leave it enough time for the commit, the wait for the next stage and its address arithmetic.
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, true) | (p.a_e5m2 ? (1u << 7) : 0u) |
-                                   (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
+            const bool bk = p.b_kmajor != 0u;
+            const uint32_t idesc = make_idesc_mxf8(kGemmBlockM, BLOCK_N, !bk) | ((p.a_fmt & 7u) << 7) |
+                                   ((p.b_fmt & 7u) << 10);  // operand formats: E4M3 = 0, E5M2 = 1, E2M1 = 5
             const uint32_t ksplit = p.ksplit > 1u ? p.ksplit : 1u;
             const uint32_t kper = k_tiles / ksplit;  // K tiles per work unit (the host only splits evenly)
             const uint32_t num_units = num_tiles * ksplit;
@@ -422,11 +568,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // B: MN-major, 128-byte swizzle: 128 columns contiguous, K rows 128 bytes apart, 8-row K groups
             // 1024 bytes apart (SBO), 128-column groups 16 KiB apart (LBO).
             const uint32_t hi_a = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
-            const uint32_t hi_b = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
+            const uint32_t hi_b = bk ? hi_a : (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
             const uint32_t a_lo0 = (uint32_t)make_smem_desc(0, 16, 1024, 2) | (smem_u32(smem + S::kOffA) >> 4);
-            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
-            constexpr uint32_t kKbStepA = 32u >> 4;    // 32 bytes along K
-            constexpr uint32_t kKbStepB = 4096u >> 4;  // 32 K rows of 128 bytes
+            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, bk ? 16 : 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
+            constexpr uint32_t kKbStepA = 32u >> 4;                // 32 bytes along K
+            const uint32_t kKbStepB = (bk ? 32u : 4096u) >> 4;     // 32 bytes along K, or 32 K rows of 128 bytes
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
             bool alive = true;
 
@@ -785,6 +931,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 store_c_chunk<OutT>(c, p, row, n0 + chunk * 32u, r);
             }
+            publish_tile_rows<OutT>(p, m0 + q * 32u, tc.n_tile, n_tiles, lane);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {

@@ -143,6 +143,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }                     // with flags, the flags say when its rows are there
         uint32_t it = 0, ti = 0;
         bool alive = true;
+        // packed 4-bit operands arrive as half the bytes they occupy in shared memory (the gaps are not written)
+        const uint32_t tx_bytes = (p.a_fmt == 5u ? S::kABytes / 2u : S::kABytes) + (p.b_fmt == 5u ? S::kBBytes / 2u : S::kBBytes);
         for (uint32_t tile = pair; alive && tile < num_tiles; tile += num_pairs, ++ti) {
             TileCoord tc = pair_tile_coord(tile, n_tiles, m_tiles, p);
             const uint32_t m0 = tc.m_tile * kPairBlockM + cta * 128u;
@@ -174,11 +176,16 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     CATCCOS_TR_STAMP_FIRST(p.trace, kTrProdFirstTma);
                     const uint32_t leader_bar = map_to_cta(smem_u32(&full[s]), 0);
-                    mbar_arrive_expect_tx_cluster(leader_bar, S::kABytes + S::kBBytes);
+                    mbar_arrive_expect_tx_cluster(leader_bar, tx_bytes);
                     tma_load_2d_pair(smem + S::kOffA + s * S::kABytes, &tmap_a, leader_bar, (int32_t)(kt * kGemmBlockK),
                                      (int32_t)m0);
-                    tma_load_2d_pair(smem + S::kOffB + s * S::kBBytes, &tmap_b, leader_bar, (int32_t)n0,
-                                     (int32_t)(kt * kGemmBlockK));
+                    if (p.b_kmajor) {  // the transposed copy [N, K]: this CTA's 128 columns are 128 rows of it
+                        tma_load_2d_pair(smem + S::kOffB + s * S::kBBytes, &tmap_b, leader_bar, (int32_t)(kt * kGemmBlockK),
+                                         (int32_t)n0);
+                    } else {
+                        tma_load_2d_pair(smem + S::kOffB + s * S::kBBytes, &tmap_b, leader_bar, (int32_t)n0,
+                                         (int32_t)(kt * kGemmBlockK));
+                    }
                     CATCCOS_TR_STAMP(p.trace, kTrProdLastTma);
                 }
                 alive = __all_sync(0xFFFFFFFFu, alive);
@@ -188,16 +195,18 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------- MMA issuer (leader CTA only) ---------------------
         // As in the single-CTA kernel the issuer issues the MMAs and the stage-releasing commit, nothing else.
         if (cta == 0 && lane == 0) {
-            const uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, true) | (p.a_e5m2 ? (1u << 7) : 0u) |
-                                   (p.b_e5m2 ? (1u << 10) : 0u);  // operand formats: E4M3 = 0, E5M2 = 1
+            const bool bk = p.b_kmajor != 0u;
+            const uint32_t idesc = make_idesc_mxf8(kPairBlockM, kPairBlockN, !bk) | ((p.a_fmt & 7u) << 7) |
+                                   ((p.b_fmt & 7u) << 10);  // operand formats: E4M3 = 0, E5M2 = 1, E2M1 = 5
             const uint32_t my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
             const uint32_t total_it = my_tiles * k_tiles;
 
             const uint32_t hi_a = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
-            const uint32_t hi_b = (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
+            const uint32_t hi_b = bk ? hi_a : (uint32_t)(make_smem_desc(0, 16384, 1024, 2) >> 32);
             const uint32_t a_lo0 = (uint32_t)make_smem_desc(0, 16, 1024, 2) | (smem_u32(smem + S::kOffA) >> 4);
             // each CTA holds 128 columns of B (one 128-byte swizzle row per K): MN-major
-            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
+            const uint32_t b_lo0 = (uint32_t)make_smem_desc(0, bk ? 16 : 16384, 1024, 2) | (smem_u32(smem + S::kOffB) >> 4);
+            const uint32_t kb_step_b = (bk ? 32u : 4096u) >> 4;
             const uint32_t sf_tmem0 = tmem_base + S::kSfCol;
 
             bool alive = true;
@@ -209,7 +218,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 CATCCOS_TR_ADD(p.trace, kTrMmaFullWaitNs, CATCCOS_TR_NOW() - t0);
             };
             auto issue_mma = [&](uint32_t a_lo, uint32_t b_lo, uint32_t sf, uint32_t kb, uint32_t d_col, uint32_t accumulate) {
-                umma_mxf8_pair_lohi(d_col, a_lo + kb * (32u >> 4), hi_a, b_lo + kb * (4096u >> 4), hi_b,
+                umma_mxf8_pair_lohi(d_col, a_lo + kb * (32u >> 4), hi_a, b_lo + kb * kb_step_b, hi_b,
                                     idesc_with_sf_id(idesc, kb), sf, sf + 4, accumulate);
             };
 
@@ -427,29 +436,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         mbar_arrive_cluster(map_to_cta(smem_u32(&overlap_free[acc]), 0));
                     }
                 }
-                const uint32_t col = n0 + chunk * 32u;
-                if (row < p.Mg && col < p.N) {
-                    OutT* dst = c + (size_t)row * p.N + col;
-                    if (col + 32u <= p.N) {
-#pragma unroll
-                        for (uint32_t v = 0; v < 2; ++v) {
-                            uint32_t o[8];
-#pragma unroll
-                            for (uint32_t e = 0; e < 8; ++e) {
-                                o[e] = pack2<OutT>(__uint_as_float(r[v * 16 + 2 * e]), __uint_as_float(r[v * 16 + 2 * e + 1]));
-                            }
-                            st_global_v8(dst + v * 16, o);  // one full 32-byte sector per store
-                        }
-                    } else {
-#pragma unroll
-                        for (uint32_t jj = 0; jj < 32u; ++jj) {
-                            if (col + jj < p.N) {
-                                dst[jj] = static_cast<OutT>(__uint_as_float(r[jj]));
-                            }
-                        }
-                    }
-                }
+                store_c_chunk<OutT>(c, p, row, n0 + chunk * 32u, r);
             }
+            publish_tile_rows<OutT>(p, m0 + q * 32u, tc.n_tile, n_tiles, lane);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {

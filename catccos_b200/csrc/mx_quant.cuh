@@ -712,6 +712,92 @@ __global__ void __launch_bounds__(kQuantThreads, 2) mx_quant_push_ordered_kernel
 #endif
 }
 
+// Routing-side producer of a packed MoE dispatch: every token (a bf16 row of N values) is quantised once and the
+// same packed row is written to each of its top_k destinations.  A packed row is
+// [N E4M3 codes | ceil(N / 32) E8M0 scales, padded to an even count | zero padding to a multiple of 32 bytes];
+// expanded_row_idx[token * top_k + route] names the destination row, a negative entry drops the route.
+// It replaces CommBlockMxQuant::QuantScatterPacked (include/catccos/comm/block/comm_block_mx_quant.hpp:312-368).
+// One warp per token; a lane quantises 16 consecutive values per 512-column step (two lanes share a 32-block).
+__host__ __device__ __forceinline__ uint32_t packed_row_bytes(uint32_t n)
+{
+    const uint32_t scale_bytes = ((n + 31u) / 32u + 1u) / 2u * 2u;
+    return (n + scale_bytes + 31u) / 32u * 32u;
+}
+
+__global__ void __launch_bounds__(kQuantThreads) mx_quant_scatter_packed_kernel(const uint16_t* __restrict__ in,
+                                                                               const int32_t* __restrict__ expanded_row_idx,
+                                                                               uint8_t* __restrict__ packed_out, uint32_t tokens,
+                                                                               uint32_t n, uint32_t top_k, uint32_t device_tiny)
+{
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row_bytes = packed_row_bytes(n);
+    const uint32_t scale_raw = n / 32u;
+    for (uint32_t token = blockIdx.x * (kQuantThreads / 32) + warp; token < tokens; token += gridDim.x * (kQuantThreads / 32)) {
+        for (uint32_t cb = 0; cb < n; cb += kQuantColsPerWarpStep) {
+            const uint32_t col = cb + lane * 16;
+            const bool ok = col < n;
+            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+            if (ok) {
+                const uint4* src = reinterpret_cast<const uint4*>(in + (size_t)token * n + col);
+                v0 = __ldcs(src);
+                v1 = __ldcs(src + 1);
+            }
+            uint32_t byte;
+            const uint4 o = quant16(v0, v1, device_tiny != 0u, false, byte);
+            for (uint32_t route = 0; route < top_k; ++route) {
+                const int32_t dst = expanded_row_idx[(size_t)token * top_k + route];
+                if (dst < 0 || !ok) {
+                    continue;
+                }
+                uint8_t* row = packed_out + (size_t)dst * row_bytes;
+                *reinterpret_cast<uint4*>(row + col) = o;
+                if ((lane & 1u) == 0u) {
+                    row[n + col / 32u] = (uint8_t)byte;
+                }
+            }
+        }
+        // the tail of the row: the scale count rounded up to even, then zeros up to the 32-byte boundary
+        for (uint32_t route = 0; route < top_k; ++route) {
+            const int32_t dst = expanded_row_idx[(size_t)token * top_k + route];
+            if (dst < 0) {
+                continue;
+            }
+            uint8_t* row = packed_out + (size_t)dst * row_bytes;
+            for (uint32_t b = n + scale_raw + lane; b < row_bytes; b += 32) {
+                row[b] = 0;
+            }
+        }
+    }
+}
+
+// Transposed copy of a packed E2M1 weight: in [K, N/2] (two N-neighbours per byte, low nibble = even column, the
+// reference's file layout, examples/utils/gen_data_fp4_mx_allgather_matmul.py:521-544) -> out [N, K/2] (two
+// K-neighbours per byte).  The tensor core reads 4-bit operands K-major only.  64 x 64 values per CTA.
+__global__ void __launch_bounds__(256) fp4_transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t K,
+                                                            uint32_t N)
+{
+    __shared__ uint8_t tile[64][65];  // one value per byte
+    const uint32_t k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
+        const uint32_t r = i / 32, cb = i % 32;  // row of K, byte of N
+        const uint32_t k = k0 + r, n = n0 + cb * 2;
+        uint8_t b = 0;
+        if (k < K && n < N) {
+            b = in[(size_t)k * (N / 2) + n / 2];
+        }
+        tile[r][cb * 2] = b & 0x0F;
+        tile[r][cb * 2 + 1] = b >> 4;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
+        const uint32_t c = i / 32, kb = i % 32;  // row of N, byte of K
+        const uint32_t n = n0 + c, k = k0 + kb * 2;
+        if (n < N && k < K) {
+            out[(size_t)n * (K / 2) + k / 2] = (uint8_t)(tile[kb * 2][c] | (tile[kb * 2 + 1][c] << 4));
+        }
+    }
+}
+
 // bf16 [rows, K] -> FP4 E2M1 codes, two per byte (low nibble = even column), + one E8M0 scale per 32 elements.
 // The FP4 branch of the reference's quantiser (include/catccos/comm/block/comm_block_mx_quant.hpp:525-568, emax
 // constant block_epilogue_dynamic_mx_quant.hpp:53): the same exponent rule with emax 2, saturation at +-6,

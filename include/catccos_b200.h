@@ -58,8 +58,9 @@ int catccos_b200_finalize(void);
 int catccos_b200_symm_alloc(size_t bytes, void** local_ptr);
 /* shmem_free (main.cpp:219). */
 int catccos_b200_symm_free(void* local_ptr);
-/* CatccosOperator::GetSymmetricSize (utils/catccos_operator.h:43): bytes the two operators need
- * for a problem (header + two stages of the gathered codes and scales). */
+/* CatccosOperator::GetSymmetricSize (utils/catccos_operator.h:43): bytes an operator needs for a problem.
+ * quant_op 0 = AllGather-Matmul, 1 = quantise + AllGather (header + two stages of the gathered codes and scales),
+ * 2 = Matmul + ReduceScatter (header + two stages of the fp32 product). */
 size_t catccos_b200_symm_bytes_needed(const catccos_b200_tiling_t* tiling, int quant_op);
 
 /* ---- operators -----------------------------------------------------------------------------
@@ -88,6 +89,18 @@ int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void
 int catccos_b200_mx_quant_allgather_matmul(void* stream, const void* a_bf16, const void* b, const void* b_scale,
                                            void* c, void* symm, const catccos_b200_tiling_t* tiling, uint32_t magic);
 
+/* DeviceDGemm<MatmulReduceScatterMxTla>::Arguments + Run, the row-parallel partner of the operator above
+ * (include/catccos/dgemm/kernel/matmul_reduce_scatter_mx_tla.hpp:36-135,
+ * examples/ascend950_mxfp8_matmul_reduce_scatter/): every rank holds its K slice, a [m, k] and b [k, n] in MXFP8
+ * with a_scale [m, k/32] and b_scale [k/64, n, 2]; the products are added over the ranks and rank r receives rows
+ * [r * m / rankSize, (r + 1) * m / rankSize) as d [m / rankSize, n] (bf16, or fp16 with "c_dtype" = 1).
+ * tiling->m is the WHOLE m, as in the reference's Arguments.  The GEMM's epilogue sends fp32 partial rows straight to
+ * the stage of the rank that owns them; that rank adds them in rank order (the result does not depend on timing).
+ * symm: catccos_b200_symm_bytes_needed(tiling, 2) bytes.  m / rankSize % 32 == 0, k % 128 == 0, n % 16 == 0. */
+int catccos_b200_mxfp8_matmul_reduce_scatter(void* stream, const void* a, const void* b, const void* a_scale,
+                                             const void* b_scale, void* d, void* symm,
+                                             const catccos_b200_tiling_t* tiling, uint32_t magic);
+
 /* ---- single-GPU building blocks (the compute halves, also the unfused baseline) ------------ */
 
 /* CommBlockMxQuant::operator() (include/catccos/comm/block/comm_block_mx_quant.hpp:155-207):
@@ -105,6 +118,23 @@ int catccos_b200_mx_quant_fp4(void* stream, const void* in_bf16, uint32_t rows, 
  * (ascend950_fp8_mx_allgather_matmul_device.h:47-57): c [m, n] = dequant(a)[m, k] x dequant(b)[k, n]. */
 int catccos_b200_mx_gemm(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,
                          uint32_t m, uint32_t n, uint32_t k);
+
+/* The same GEMM with the MX quantiser in its epilogue: every 32 consecutive output columns of a row are rounded to
+ * bf16, quantised (E4M3 codes + one E8M0 scale) and written as c_codes [m, n] and c_scales [m, n/32]; the 16-bit
+ * tensor is never materialised.  CommBlockMxQuant::QuantFromUb / QuantFromUb2D
+ * (include/catccos/comm/block/comm_block_mx_quant.hpp:209-310), the reference's quantise-in-epilogue producer.
+ * n % 32 == 0.  The result equals catccos_b200_mx_quant applied to the bf16 output of catccos_b200_mx_gemm. */
+int catccos_b200_mx_gemm_quant_out(void* stream, const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                   void* c_codes, void* c_scales, uint32_t m, uint32_t n, uint32_t k);
+
+/* CommBlockMxQuant::QuantScatterPacked (comm_block_mx_quant.hpp:312-368), the routing-side producer of the packed
+ * MoE dispatch: token t (bf16 [n]) is quantised once and its packed row is written to rows
+ * expanded_row_idx[t * top_k + r], r < top_k, of packed_out (negative entries drop the route).  A packed row is
+ * [n E4M3 codes | n/32 E8M0 scales, padded to an even count | zeros to a multiple of 32 bytes];
+ * catccos_b200_packed_row_bytes(n) is its length.  n % 32 == 0; in_bf16 and packed_out 16-byte aligned. */
+size_t catccos_b200_packed_row_bytes(uint32_t n);
+int catccos_b200_mx_quant_scatter_packed(void* stream, const void* in_bf16, const int32_t* expanded_row_idx, void* packed_out,
+                                         uint32_t tokens, uint32_t n, uint32_t top_k);
 
 /* Fused quantise + matmul on one GPU that allocates nothing.  It has no counterpart in the reference.
  * c [m, n] = dequant(quantise(a_bf16 [m, k])) x dequant(b [k, n], b_scale [k/64, n, 2]): the same two

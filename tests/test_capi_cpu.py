@@ -40,9 +40,9 @@ def test_set_option_rejects_unknown(capi):
     assert capi.load().catccos_b200_set_option(b"no_such_option", 1) == -1
     assert capi.load().catccos_b200_set_option(b"block_n", 192) == -1
     assert capi.load().catccos_b200_set_option(b"block_n", 0) == 0
-    for key in (b"tiny_block_rule", b"c_dtype", b"a_dtype", b"b_dtype"):  # the public keys
+    for key, bad in ((b"tiny_block_rule", 2), (b"c_dtype", 2), (b"a_dtype", 3), (b"b_dtype", 3)):  # the public keys
         assert capi.load().catccos_b200_set_option(key, 0) == 0
-        assert capi.load().catccos_b200_set_option(key, 2) == -1
+        assert capi.load().catccos_b200_set_option(key, bad) == -1
     assert capi.load().catccos_b200_set_option(b"timeout_ms", 2000) == 0
 
 

@@ -224,3 +224,49 @@ def test_pair_shapes(capi, cuda, oracle, m, n, k):
     _check(oracle, out, gold, k)
     out16 = _run(capi, cuda, ac, asc, bc, bsc, cta_pair=1, f16=True)
     assert oracle.check_reference_rule(out16, gold, k, bf16=False)[0] == 0
+
+
+# ---- FP4 (E2M1) operands, packed two per byte: the reference's float4_e2m1x2_t operator variant
+# (examples/ascend950_fp4_mx_allgather_matmul/ascend950_fp4_mx_allgather_matmul_device.h:42-49) ----
+
+def _fp4_weight(oracle, b_f32):
+    """B [K, N] -> packed E2M1 [K, N/2] (low nibble = even column, as gen_data_fp4_mx_allgather_matmul.py:521-544
+    packs it), scales [K/64, N, 2] (32 along K), and the dequantised fp32 matrix."""
+    k, n = b_f32.shape
+    pt, st = oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(np.ascontiguousarray(b_f32.T)))  # [N, K/2], [N, K/32]
+    deq = oracle.dequant_rows_e2m1(pt, st).T.copy()
+    nib = np.empty((n, k), np.uint8)
+    nib[:, 0::2] = pt & 0x0F
+    nib[:, 1::2] = pt >> 4
+    nib = np.ascontiguousarray(nib.T)  # [K, N]
+    packed = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    scales = np.ascontiguousarray(st.T.reshape(k // 64, 2, n).transpose(0, 2, 1))
+    return packed, scales, deq
+
+
+@pytest.mark.parametrize("cta_pair", [2, 1])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (300, 512, 2048), (1024, 2304, 7168)])
+def test_fp4_operands(capi, cuda, oracle, m, n, k, cta_pair):
+    torch = cuda
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.02)
+    ap, asc = oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(a))
+    bp, bsc, b_deq = _fp4_weight(oracle, b)
+    gold = oracle.gemm_f32(oracle.dequant_rows_e2m1(ap, asc), b_deq)
+    capi.set_option("a_dtype", 2)
+    capi.set_option("b_dtype", 2)
+    capi.set_option("cta_pair", cta_pair)
+    try:
+        c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        dev = [torch.from_numpy(x).cuda() for x in (ap, asc, bp, bsc)]  # kept alive until the kernel has run
+        rc = capi.load().catccos_b200_mx_gemm(torch.cuda.current_stream().cuda_stream, dev[0].data_ptr(), dev[1].data_ptr(),
+                                               dev[2].data_ptr(), dev[3].data_ptr(), c.data_ptr(), m, n, k)
+        assert rc == 0
+        code, st = capi.last_status()
+        assert code == 0, st
+        _check(oracle, c.float().cpu().numpy(), gold, k)
+    finally:
+        capi.set_option("a_dtype", 0)
+        capi.set_option("b_dtype", 0)
+        capi.set_option("cta_pair", 0)
