@@ -25,6 +25,7 @@ EXPORTS = [
     "catccos_b200_symm_bytes_needed",
     "catccos_b200_mx_quant_allgather",
     "catccos_b200_fp8_mx_allgather_matmul",
+    "catccos_b200_fp4_mx_allgather_matmul",
     "catccos_b200_mx_quant_allgather_matmul",
     "catccos_b200_mx_quant",
     "catccos_b200_mx_quant_fp4",
@@ -84,6 +85,7 @@ def load() -> ctypes.CDLL:
     L.catccos_b200_symm_bytes_needed.restype = sz
     L.catccos_b200_mx_quant_allgather.argtypes = [vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_fp8_mx_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, vp, tp, u32]
+    L.catccos_b200_fp4_mx_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant_allgather_matmul.argtypes = [vp, vp, vp, vp, vp, vp, tp, u32]
     L.catccos_b200_mx_quant.argtypes = [vp, vp, u32, u32, vp, vp]
     L.catccos_b200_mx_quant_fp4.argtypes = [vp, vp, u32, u32, vp, vp]
@@ -329,5 +331,16 @@ def fp8_mx_allgather_matmul(a_codes, a_scales, b, b_scales, c, symm: int, world:
     t = make_tiling(m, k, n, world)
     _check("catccos_b200_fp8_mx_allgather_matmul",
            load().catccos_b200_fp8_mx_allgather_matmul(_stream(), a_codes.data_ptr(), b.data_ptr(),
+                                                       a_scales.data_ptr(), b_scales.data_ptr(), c.data_ptr(), symm,
+                                                       ctypes.byref(t), 0))
+
+
+def fp4_mx_allgather_matmul(a_packed, a_scales, b_packed, b_scales, c, symm: int, world: int) -> None:
+    """The FP4 operator: a packed E2M1 [m, k/2], b packed E2M1 [k, n/2]."""
+    m, k = a_packed.shape[0], a_packed.shape[1] * 2
+    n = b_scales.shape[1]
+    t = make_tiling(m, k, n, world)
+    _check("catccos_b200_fp4_mx_allgather_matmul",
+           load().catccos_b200_fp4_mx_allgather_matmul(_stream(), a_packed.data_ptr(), b_packed.data_ptr(),
                                                        a_scales.data_ptr(), b_scales.data_ptr(), c.data_ptr(), symm,
                                                        ctypes.byref(t), 0))

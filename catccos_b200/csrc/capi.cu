@@ -639,7 +639,7 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     p.b_fmt = g.b_dtype == 2 ? 5u : (g.b_dtype == 1 ? 1u : 0u);
     const bool a_fp4 = g.a_dtype == 2, b_fp4 = g.b_dtype == 2;
     if ((a_fp4 && (((uintptr_t)a & 31u) || p.K % 128 != 0)) || (b_fp4 && (((uintptr_t)b & 31u) || p.N % 128 != 0))) {
-        ERROR_LOG("mx gemm: packed E2M1 operands must be 32-byte aligned, with K (and N for B) a multiple of 128");
+        ERROR_LOG("mx gemm: packed E2M1 operands must be 32-byte aligned, with K a multiple of 128 (and N, for B)");
         return CATCCOS_B200_EINVAL;
     }
     if (b_fp4) {
@@ -733,6 +733,14 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
     return CATCCOS_B200_EINVAL;
 }
 
+// Sets n flag words to the epoch (the rows they stand for were put in place by stream-ordered copies).
+__global__ void fill_flags_kernel(uint32_t* flags, uint32_t n, uint32_t epoch)
+{
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        flags[i] = epoch;
+    }
+}
+
 // Ends once every listed flag word carries the epoch (bounded): what follows on the stream may read the rows the
 // peers' copy engines wrote.  One thread per word.
 __global__ void wait_flags_kernel(const uint32_t* flags, uint32_t flag_stride, uint32_t world, uint32_t rank, uint32_t chunks,
@@ -760,9 +768,11 @@ constexpr uint32_t kCopySliceRows = 256;  // rows the copy engines move (and fla
 // units to itself, and the slices arrive in the order the GEMM visits them.
 int copy_engine_push(RankCtx& rc, cudaStream_t st, uint32_t W, uint32_t rank, uint32_t M, uint32_t K, uint32_t segs,
                      uint32_t slice_rows, const uint8_t* src_codes, const uint8_t* src_scales, const uint32_t* src_flags,
-                     uint8_t* const* dst_codes, uint8_t* const* dst_scales, uint32_t* const* dst_flags)
+                     uint8_t* const* dst_codes, uint8_t* const* dst_scales, uint32_t* const* dst_flags,
+                     size_t code_row_bytes = 0)
 {
     const uint32_t sf = K / 32;
+    const size_t row_bytes = code_row_bytes != 0 ? code_row_bytes : K;  // a row of codes: K bytes, K / 2 for packed E2M1
     CUDA_TRY(cudaEventRecord(rc.ev_quant, st));
     for (uint32_t t = 0; t + 1 < W; ++t) {
         const uint32_t d = (rank + 1 + t) % W;
@@ -772,8 +782,8 @@ int copy_engine_push(RankCtx& rc, cudaStream_t st, uint32_t W, uint32_t rank, ui
         for (uint32_t r0 = 0; r0 < M; r0 += slice_rows) {
             const uint32_t rows = std::min(slice_rows, M - r0);
             const uint32_t c0 = r0 / kRowsPerChunk, chunks = (rows + kRowsPerChunk - 1) / kRowsPerChunk;
-            CUDA_TRY(cudaMemcpyAsync(dst_codes[d] + (size_t)r0 * K, src_codes + (size_t)r0 * K, (size_t)rows * K,
-                                     cudaMemcpyDeviceToDevice, cs));
+            CUDA_TRY(cudaMemcpyAsync(dst_codes[d] + (size_t)r0 * row_bytes, src_codes + (size_t)r0 * row_bytes,
+                                     (size_t)rows * row_bytes, cudaMemcpyDeviceToDevice, cs));
             CUDA_TRY(cudaMemcpyAsync(dst_flags[d] + (size_t)c0 * segs, src_flags + (size_t)c0 * segs,
                                      (size_t)chunks * segs * sizeof(uint32_t), cudaMemcpyDeviceToDevice, cs));
         }
@@ -1479,6 +1489,97 @@ int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void
 {
     (void)magic;
     return allgather_matmul(stream, a, a_scale, true, b, b_scale, c, symm, t);
+}
+
+int catccos_b200_fp4_mx_allgather_matmul(void* stream, const void* a, const void* b, const void* a_scale,
+                                         const void* b_scale, void* c, void* symm, const catccos_b200_tiling_t* t,
+                                         uint32_t magic)
+{
+    (void)magic;
+    if (!t || !a || !b || !a_scale || !b_scale || !c) {
+        return CATCCOS_B200_EINVAL;
+    }
+    int rcode = ensure_init();
+    if (rcode != 0) return rcode;
+    const uint32_t M = t->m, K = t->k, N = t->n, W = t->rankSize;
+    if (W != (uint32_t)g.world || M == 0 || K % kGemmBlockK != 0 || N % 16 != 0) {
+        ERROR_LOG("fp4 allgather matmul: rankSize %u (world %d), M=%u K=%u N=%u unsupported", W, g.world, M, K, N);
+        return CATCCOS_B200_EINVAL;
+    }
+    RankCtx& rc = cur();
+    CUDA_TRY(cudaSetDevice(rc.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t rank = (uint32_t)g.rank;
+    // both operands are packed E2M1 for the length of this call, whatever the options say
+    struct DtypeGuard {
+        int a, b;
+        DtypeGuard() : a(g.a_dtype), b(g.b_dtype) { g.a_dtype = 2; g.b_dtype = 2; }
+        ~DtypeGuard() { g.a_dtype = a; g.b_dtype = b; }
+    } guard;
+    GemmParams p = {};
+    p.a_scales = (const uint8_t*)a_scale;
+    p.b_scales = (const uint8_t*)b_scale;
+    p.c = c;
+    p.Mg = W * M;
+    p.N = N;
+    p.K = K;
+    p.world = W;
+    p.rank = rank;
+    p.m_local = M;
+    if (W == 1) {
+        return launch_gemm(rc, st, a, b, p);
+    }
+    SymmAlloc* sa = find_symm(symm);
+    if (sa == nullptr) {
+        ERROR_LOG("fp4 allgather matmul: symm must come from catccos_b200_symm_alloc");
+        return CATCCOS_B200_ENOTSYMM;
+    }
+    // a stage: the gathered packed codes [W * M, K / 2], then the gathered scales [W * M, K / 32]
+    const size_t row_bytes = K / 2, sf = K / 32;
+    const size_t stage_bytes = ((sa->size - kHeaderBytes) / 2) & ~(size_t)1023;
+    const size_t scales_off = align_up((size_t)W * M * row_bytes, 1024);
+    const uint32_t chunks = (M + kRowsPerChunk - 1) / kRowsPerChunk;
+    if (sa->size < kHeaderBytes + 2048 || scales_off + align_up((size_t)W * M * sf, 1024) > stage_bytes || chunks > kMaxFlags) {
+        ERROR_LOG("fp4 allgather matmul: symmetric buffer of %zu bytes too small", sa->size);
+        return CATCCOS_B200_ENOMEM;
+    }
+    const bool produce = (g.phase_mask & 1) != 0, consume = (g.phase_mask & 2) != 0;
+    if (produce) {
+        sa->epoch[g.rank] += 1;
+    }
+    const uint32_t epoch = sa->epoch[g.rank];
+    const size_t stage_off = kHeaderBytes + (size_t)(epoch & 1u) * stage_bytes;
+    uint8_t* dc[kMaxRanks] = {};
+    uint8_t* ds[kMaxRanks] = {};
+    uint32_t* df[kMaxRanks] = {};
+    for (uint32_t d = 0; d < W; ++d) {
+        uint8_t* base = sa->base[d] + stage_off;
+        dc[d] = base + (size_t)rank * M * row_bytes;
+        ds[d] = base + scales_off + (size_t)rank * M * sf;
+        df[d] = reinterpret_cast<uint32_t*>(sa->base[d] + kFlagsOff) + (size_t)rank * kMaxFlags;
+    }
+    if (produce) {
+        // A arrives quantised: this rank's shard goes into its own stage by two copies, its flag words are set,
+        // and the copy engines forward all three to the peers (one flag word per 16-row chunk, one K segment)
+        CUDA_TRY(cudaMemcpyAsync(dc[rank], a, (size_t)M * row_bytes, cudaMemcpyDeviceToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(ds[rank], a_scale, (size_t)M * sf, cudaMemcpyDeviceToDevice, st));
+        fill_flags_kernel<<<(chunks + 255) / 256, 256, 0, st>>>(df[rank], chunks, epoch);
+        g_launches++;
+        CUDA_TRY(cudaGetLastError());
+        rcode = copy_engine_push(rc, st, W, rank, M, K, 1, kCopySliceRows, dc[rank], ds[rank], df[rank], dc, ds, df, row_bytes);
+        if (rcode != 0) return rcode;
+    }
+    if (consume) {
+        p.a_scales = sa->base[rank] + stage_off + scales_off;
+        p.flags = reinterpret_cast<const uint32_t*>(sa->base[rank] + kFlagsOff);
+        p.flag_stride = kMaxFlags;
+        p.segs = 1;
+        p.seg_ktiles = K / kGemmBlockK;
+        p.epoch = epoch;
+        rcode = launch_gemm(rc, st, sa->base[rank] + stage_off, b, p);
+        if (rcode != 0) return rcode;
+    }
+    return produce ? copy_engine_join(rc, st, W) : 0;
 }
 
 int catccos_b200_mx_quant_allgather_matmul(void* stream, const void* a_bf16, const void* b, const void* b_scale,

@@ -4,7 +4,9 @@
 
 #include "../examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_device.h"
 #include "../examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_host.h"
+#include "../examples/ascend950_fp4_mx_allgather_matmul/ascend950_fp4_mx_allgather_matmul_host.h"
 #include "../examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h"
+#include "../examples/ascend950_mxfp8_matmul_reduce_scatter/ascend950_mxfp8_matmul_reduce_scatter_host.h"
 #include "dynamic_tiling/launch_map.h"
 
 #define EXPECT(cond)                                                     \
@@ -56,6 +58,25 @@ int main()
     auto q = reg.CreateOperator("MxQuantAllGather");
     auto g = reg.CreateOperator("Ascend950Fp8MxAllGatherMatmul");
     EXPECT(q != nullptr && g != nullptr);
+    {
+        // the FP4 variant and the row-parallel partner: registry names, enum ids and short names of the reference
+        auto f4 = reg.CreateOperator("Ascend950Fp4MxAllGatherMatmul");
+        auto rs = reg.CreateOperator("Ascend950MxFp8MatmulReduceScatter");
+        EXPECT(f4 != nullptr && rs != nullptr);
+        CocTilingParams s;
+        s.m = 1024;
+        s.k = 7168;
+        s.n = 2304;
+        s.rankSize = 8;
+        EXPECT(f4->GetActualKernelType(s) == 23 && GetCommType("a5fp4mxagmm") == ASCEND950_FP4_MX_ALLGATHER_MATMUL);
+        EXPECT(rs->GetActualKernelType(s) == 18 && GetCommType("a5mxfp8mmrs") == ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER);
+        EXPECT(f4->CheckCocTilingParams(8, s) && rs->CheckCocTilingParams(8, s));
+        s.n = 2320;  // a multiple of 16 but not of 128: fine for the reduce-scatter, not for packed FP4 rows
+        EXPECT(!f4->CheckCocTilingParams(8, s) && rs->CheckCocTilingParams(8, s));
+        s.m = 1000;  // 125 rows per rank
+        EXPECT(!rs->CheckCocTilingParams(8, s));
+        EXPECT(rs->GetSymmetricSize(s) > 2ull * 1000 * 2320 * 4);
+    }
     EXPECT(reg.CreateOperator("NoSuchOperator") == nullptr);
     EXPECT(!reg.RegisterOperator("MxQuantAllGather", [] { return std::unique_ptr<CatccosOperator>(); }));
 

@@ -26,11 +26,12 @@ constexpr int32_t SHMEM_BUFF_BYTES = 1004 * 1024 * 1024;  // the reference's def
 constexpr uint32_t SYNC_UNIT_SIZE = 4 * sizeof(int64_t);
 constexpr int32_t MAX_RANK_SIZE = 128;  // accepted by the shape checks; this build runs at most 8 ranks
 
-// Only the operators of the MXFP8 quantise + AllGather-Matmul path exist here; the numeric values of
-// the reference enum are kept so that ids stored by callers stay valid.
+// Only the operators of the MX quantise + AllGather-Matmul path and its row-parallel partner exist here; the
+// numeric values of the reference enum are kept so that ids stored by callers stay valid.
 enum CocCommType {
+    ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = 18,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = 22,
-    ASCEND950_FP4_MX_ALLGATHER_MATMUL = 23,  // id reserved, not built
+    ASCEND950_FP4_MX_ALLGATHER_MATMUL = 23,
     MX_QUANT_ALLGATHER = 24,
     TYPE_NUM = 45,
     UNKNOWN
@@ -145,7 +146,9 @@ inline void FreeDeviceSpace(KernelParams& params)
 }
 
 const std::map<std::string, CocCommType> CommTypeMap = {
+    {"a5mxfp8mmrs", CocCommType::ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
     {"a5fp8mxagmm", CocCommType::ASCEND950_FP8_MX_ALLGATHER_MATMUL},
+    {"a5fp4mxagmm", CocCommType::ASCEND950_FP4_MX_ALLGATHER_MATMUL},
     {"mxqtag", CocCommType::MX_QUANT_ALLGATHER},
 };
 
@@ -156,7 +159,9 @@ inline CocCommType GetCommType(const std::string& kernelName)
 }
 
 const std::map<CocCommType, std::string> CommTypeOpNameMap = {
+    {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
     {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
+    {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
     {MX_QUANT_ALLGATHER, "MxQuantAllGather"},
 };
 

@@ -83,6 +83,17 @@ int catccos_b200_fp8_mx_allgather_matmul(void* stream, const void* a, const void
                                          const void* b_scale, void* c, void* symm,
                                          const catccos_b200_tiling_t* tiling, uint32_t magic);
 
+/* The FP4 variant of the operator above: DeviceDGemm<MxAllGatherMatmulTla> composed with float4_e2m1x2_t operands
+ * (examples/ascend950_fp4_mx_allgather_matmul/ascend950_fp4_mx_allgather_matmul_device.h:42-104).
+ * a packed E2M1 [m, k/2] and b packed E2M1 [k, n/2] (two values per byte, low nibble = even column, the layout
+ * examples/utils/gen_data_fp4_mx_allgather_matmul.py:521-544 writes); a_scale E8M0 [m, k/32]; b_scale E8M0
+ * [k/64, n, 2]; c [rankSize*m, n].  The shards travel by the copy engines; the GEMM reads the packed codes through
+ * TMA (unpacked on the way into shared memory) and runs tcgen05.mma kind::mxf8f6f4 with E2M1 operands.
+ * k % 128 == 0, n % 128 == 0; a and b 32-byte aligned. */
+int catccos_b200_fp4_mx_allgather_matmul(void* stream, const void* a, const void* b, const void* a_scale,
+                                         const void* b_scale, void* c, void* symm,
+                                         const catccos_b200_tiling_t* tiling, uint32_t magic);
+
 /* The fused form of the two operators above (quantise kernel pushes, GEMM kernel consumes as
  * chunks land): a bf16 [m, k] quantised on the fly, everything else as above.  The reference has
  * no single entry point for it; it is MxQuantAllGather feeding MxAllGatherMatmulTla. */
@@ -178,8 +189,11 @@ int catccos_b200_last_status(uint32_t out[4]);
  *   "c_dtype"         0 = bf16, 1 = fp16 (the reference's output type, main.cpp:28)
  *   "a_dtype"         element type of the A codes, written by the quantiser and read by the GEMM: 0 = E4M3
  *                     (emax 8, +-448), 1 = E5M2 (emax 15, +-57344; MX_QUANT_DTYPE = 1 in the reference,
- *                     comm_block_mx_quant.hpp:75-76,410)
- *   "b_dtype"         element type of the B codes the caller passes: 0 = E4M3, 1 = E5M2
+ *                     comm_block_mx_quant.hpp:75-76,410), 2 = packed E2M1 (catccos_b200_mx_gemm only: a is
+ *                     [m, k/2]; the fused quantisers write 8-bit codes)
+ *   "b_dtype"         element type of the B codes the caller passes: 0 = E4M3, 1 = E5M2, 2 = packed E2M1
+ *                     [k, n/2] (transposed into a per-rank scratch on every call: the tensor core reads 4-bit
+ *                     operands K-major only)
  *   "timeout_ms"      limit of device-side waits on peers (default 2000)
  * Any other key is rejected with CATCCOS_B200_EINVAL, except the test hooks that
  * catccos_b200/csrc/internal_options.h lists (they force kernel variants and are not part of this boundary).

@@ -313,3 +313,37 @@ def test_prefill_shape_at_full_size_emulated(capi, cuda, oracle, local_world, wo
             out = c_d[r][torch.from_numpy(rows).cuda()].float().cpu().numpy()
             bad, maxdiff = oracle.check_close(out, gold, 1e-2, 1e-3)
             assert bad == 0, (rnd, r, bad, maxdiff)
+
+
+@pytest.mark.parametrize("world,m,k,n", [(1, 256, 512, 256), (2, 128, 1024, 512), (4, 272, 2048, 384)])
+def test_fp4_allgather_matmul_emulated(capi, cuda, oracle, local_world, world, m, k, n):
+    # the reference's FP4 operator: both operands packed E2M1 (two per byte), E8M0 scales per 32 along K
+    torch = cuda
+    local_world(world)
+    symm = _alloc_symm(capi, world, capi.symm_bytes_needed(capi.make_tiling(m, k, n, world), False))
+    rng = np.random.default_rng(world + m + k)
+    for rnd in range(2):
+        aq = [oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+              for _ in range(world)]
+        a_deq = np.concatenate([oracle.dequant_rows_e2m1(p, s) for p, s in aq])
+        bw = []
+        for _ in range(world):
+            b = rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.05)
+            pt, st = oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(np.ascontiguousarray(b.T)))  # [N, K/2], [N, K/32]
+            nib = np.empty((n, k), np.uint8)
+            nib[:, 0::2] = pt & 0x0F
+            nib[:, 1::2] = pt >> 4
+            nib = np.ascontiguousarray(nib.T)
+            bw.append(((nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8),
+                       np.ascontiguousarray(st.T.reshape(k // 64, 2, n).transpose(0, 2, 1)),
+                       oracle.dequant_rows_e2m1(pt, st).T.copy()))
+        a_d = [(torch.from_numpy(p).cuda(), torch.from_numpy(s).cuda()) for p, s in aq]
+        b_d = [(torch.from_numpy(x[0]).cuda(), torch.from_numpy(x[1]).cuda()) for x in bw]
+        c_d = [torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        _agmm_round(capi, torch,
+                    lambda r: capi.fp4_mx_allgather_matmul(a_d[r][0], a_d[r][1], b_d[r][0], b_d[r][1], c_d[r], symm[r], world),
+                    world)
+        for r in range(world):
+            gold = oracle.gemm_f32(a_deq, bw[r][2])
+            bad, maxdiff = oracle.check_close(c_d[r].float().cpu().numpy(), gold, 1e-2, 1e-3)
+            assert bad == 0, (rnd, r, bad, maxdiff)
