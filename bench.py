@@ -517,9 +517,10 @@ def run_gpu(args) -> None:
             "weight_stream_floor_us": (dcfg.k * dcfg.n_local * 33 / 32) / read_peaks()["hbm_gbs"] / 1e3,
         }
 
-    leg("quant_allgather", quant_allgather_leg)
-    leg("decode_c5", decode_leg)
-    leg("unfused_baseline", unfused_leg)
+    if not args.lean:
+        leg("quant_allgather", quant_allgather_leg)
+        leg("decode_c5", decode_leg)
+        leg("unfused_baseline", unfused_leg)
     code, st = capi.last_status()
     if code != 0:
         raise SystemExit(f"device-side wait ran out in an extra leg: {st}")
@@ -558,7 +559,7 @@ def run_gpu(args) -> None:
             "achieved_from": "2*(world*m_local)*k*n_local FLOP per launch / CUDA-event time of the GEMM kernel: "
                              + ("timed alone on the step's quantised operands (the step is quantise kernel, then GEMM kernel)"
                                 if world == 1 else
-                                "the kernel spans the step (the quantise-and-push warps ride inside it)"),
+                                "the step time: the flag-gated kernel's span depends on when its rows arrive"),
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(a_host[0].numel() * 2), "d2h_bytes_per_step": int(c_host[0].numel() * 2),
@@ -570,7 +571,7 @@ def run_gpu(args) -> None:
         **extras,
     }
     if rank == 0:
-        if world == 1:
+        if world == 1 and not args.lean:
             line["cpu_baseline"] = run_cpu_baseline(1)
         print(json.dumps(line))
     barrier()
@@ -636,6 +637,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--lean", action="store_true",
+                    help="headline step, end-to-end and parity only (no extra legs, no CPU baseline): the launch-list capture")
     ap.add_argument("--kernel", choices=["gemm", "quant"], default=None,
                     help="time one kernel alone on one GPU instead of the benchmark (shape: --m --n --k)")
     ap.add_argument("--m", type=int, default=8192)
