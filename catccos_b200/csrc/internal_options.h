@@ -11,7 +11,7 @@
 #define CATCCOS_B200_OPT_PHASE_MASK "phase_mask"
 // 0 = automatic, 1 = always run the GEMM on CTA pairs (256 x 256 tiles, cta_group::2), 2 = never
 #define CATCCOS_B200_OPT_CTA_PAIR "cta_pair"
-// -1 = automatic (3 with one rank; with several, 6 for shards of half a MiB and more per peer, else 0);
+// -1 = automatic (3 with one rank, 6 with several);
 // 0 = quantise and pusher warps inside the GEMM kernel (one launch); 3 = one rank only: quantise kernel, then GEMM
 // kernel on the same stream; 4 = quantise kernel into the local stage, then the GEMM kernel whose pusher warps
 // forward the stage to the peers; 5 = quantise kernel, copy engines forward the stage slice by slice, flag-gated
@@ -22,3 +22,6 @@
 // 0 = automatic (K is cut in up to eight parts when the output tiles would leave half of the SMs idle),
 // 1 = never, 2..8 = at most that many parts
 #define CATCCOS_B200_OPT_SPLIT_K "split_k"
+// order in which a flag-gated GEMM visits its row tiles: -1 = automatic (follows fuse_mode), 1 = this rank's own
+// shard first, then the peers slice by slice, 0 = slice by slice over all ranks, own slice leading
+#define CATCCOS_B200_OPT_TILE_ORDER "tile_order"

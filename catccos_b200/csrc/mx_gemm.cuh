@@ -80,6 +80,9 @@ struct GemmParams {
     uint32_t segs, seg_ktiles;
     uint32_t world, rank, m_local, epoch;
     uint32_t gemm_off;        // 1: the GEMM warps stay idle (the producer half of a call, run apart)
+    uint32_t own_first;       // tile order of a gated launch: 1 = this rank's whole shard first (it is there before any
+                              // peer's rows), 0 = slice by slice over ALL ranks, own slice leading (every rank's
+                              // rows, this rank's included, are produced at the pace of the transfer)
     uint64_t timeout_ns;      // limit of a wait for ready flags
     uint64_t bar_timeout_ns;  // limit of a wait on an intra-kernel barrier (set above timeout_ns by the host)
     StatusBlock* status;
@@ -133,8 +136,21 @@ struct TileCoord {
 };
 
 // Tile visiting order.  n runs fastest so that concurrently running CTAs share one A panel in L2.
-// With gating, m tiles follow arrival: this rank's own shard first, then for each 128-row slice of
-// a shard, the peers in ring order starting after this rank.
+// With gating, m tiles follow arrival.  own_first: this rank's own shard, then for each 128-row slice of a
+// shard, the peers in ring order starting after this rank.  Otherwise slice by slice over all ranks, this
+// rank's slice leading and the peers behind it in ring order.
+__host__ __device__ __forceinline__ uint32_t arrival_m_tile(uint32_t mo, uint32_t tps, const GemmParams& p)
+{
+    if (p.own_first == 0u) {
+        return ((p.rank + mo % p.world) % p.world) * tps + mo / p.world;
+    }
+    if (mo < tps) {
+        return p.rank * tps + mo;
+    }
+    const uint32_t j = mo - tps;
+    return ((p.rank + 1 + j % (p.world - 1)) % p.world) * tps + j / (p.world - 1);
+}
+
 __host__ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t n_tiles, uint32_t m_tiles, const GemmParams& p)
 {
     uint32_t mo = idx / n_tiles;
@@ -142,15 +158,7 @@ __host__ __device__ __forceinline__ TileCoord tile_coord(uint32_t idx, uint32_t 
     t.n_tile = idx - mo * n_tiles;
     if (p.flags != nullptr && p.world > 1) {
         if (p.m_local % kGemmBlockM == 0) {
-            uint32_t tps = p.m_local / kGemmBlockM;
-            if (mo < tps) {
-                t.m_tile = p.rank * tps + mo;
-            } else {
-                uint32_t j = mo - tps;
-                uint32_t mt = j / (p.world - 1);
-                uint32_t src = (p.rank + 1 + j % (p.world - 1)) % p.world;
-                t.m_tile = src * tps + mt;
-            }
+            t.m_tile = arrival_m_tile(mo, p.m_local / kGemmBlockM, p);
         } else {
             uint32_t first = (p.rank * p.m_local) / kGemmBlockM;
             t.m_tile = (mo + first) % m_tiles;

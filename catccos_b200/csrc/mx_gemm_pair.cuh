@@ -56,15 +56,7 @@ __host__ __device__ __forceinline__ TileCoord pair_tile_coord(uint32_t idx, uint
     t.m_tile = mo;
     if (p.flags != nullptr && p.world > 1) {
         if (p.m_local % kPairBlockM == 0) {
-            const uint32_t tps = p.m_local / kPairBlockM;
-            if (mo < tps) {
-                t.m_tile = p.rank * tps + mo;
-            } else {
-                const uint32_t j = mo - tps;
-                const uint32_t mt = j / (p.world - 1);
-                const uint32_t src = (p.rank + 1 + j % (p.world - 1)) % p.world;
-                t.m_tile = src * tps + mt;
-            }
+            t.m_tile = arrival_m_tile(mo, p.m_local / kPairBlockM, p);
         } else {
             t.m_tile = (mo + (p.rank * p.m_local) / kPairBlockM) % m_tiles;
         }

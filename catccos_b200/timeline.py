@@ -104,9 +104,12 @@ def main():
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="library option (test hooks included)")
     ap.add_argument("--label", default="")
     ap.add_argument("--raw", default="", help="also save every rank's raw [CTAs, slots] array to this .npz")
-    ap.add_argument("--sweep", default="", metavar="KEY=V1,V2,...",
+    ap.add_argument("--sweep", action="append", default=[], metavar="KEY=V1,V2,...",
                     help="no timeline: time the step (20 launches, slowest rank per launch) under every value of one "
-                         "option, in one process; works with the product build too")
+                         "option, in one process; given more than once, under every combination; works with the "
+                         "product build too")
+    ap.add_argument("--also-shape", action="append", default=[], metavar="M,K,N",
+                    help="with --sweep: one more per-rank shape to run the same sweep on (may be repeated)")
     args = ap.parse_args()
     if not capi.TRACE and not args.sweep:
         raise SystemExit("set CATCCOS_B200_TRACE=1: the timeline needs the trace build of the library")
@@ -133,52 +136,67 @@ def main():
         capi.set_option(key, int(val))
     progress("library initialised")
 
-    cfg = workloads.Config("timeline", args.m, args.k, args.n, (world,), "normal", "")
-    a = torch.from_numpy(workloads.activation_bits(cfg, rank, seed=0).view(np.int16).copy()).to(dev).view(torch.bfloat16)
-    wt = torch.from_numpy(np.ascontiguousarray(workloads.weight_bits(cfg, rank, seed=0).T).view(np.int16).copy()).to(dev).view(torch.bfloat16)
-    wc, ws = capi.mx_quant(wt)
-    b = wc.t().contiguous()
-    bs = ws.t().contiguous().view(cfg.k // 64, 2, cfg.n_local).permute(0, 2, 1).contiguous()
-    c = torch.empty((world * args.m, args.n), dtype=torch.bfloat16, device=dev)
-    symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(args.m, args.k, args.n, world), False))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     word = torch.zeros(1, device=dev)
-    progress("buffers ready")
 
-    def one(timed=False):
-        flush.fill_(1)
-        flush.view(torch.int32).sum()
-        if world > 1:
-            dist.all_reduce(word)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        capi.mx_quant_allgather_matmul(a, b, bs, c, symm, world)
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e3
+    def make_step(m, k, n):
+        """Buffers of one shape and the function that runs (and times) one step on them."""
+        cfg = workloads.Config("timeline", m, k, n, (world,), "normal", "")
+        a = torch.from_numpy(workloads.activation_bits(cfg, rank, seed=0).view(np.int16).copy()).to(dev).view(torch.bfloat16)
+        wt = torch.from_numpy(np.ascontiguousarray(workloads.weight_bits(cfg, rank, seed=0).T).view(np.int16).copy()).to(dev).view(torch.bfloat16)
+        wc, ws = capi.mx_quant(wt)
+        b = wc.t().contiguous()
+        bs = ws.t().contiguous().view(cfg.k // 64, 2, cfg.n_local).permute(0, 2, 1).contiguous()
+        c = torch.empty((world * m, n), dtype=torch.bfloat16, device=dev)
+        symm = capi.symm_alloc(capi.symm_bytes_needed(capi.make_tiling(m, k, n, world), False))
+
+        def one():
+            flush.fill_(1)
+            flush.view(torch.int32).sum()
+            if world > 1:
+                dist.all_reduce(word)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            capi.mx_quant_allgather_matmul(a, b, bs, c, symm, world)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3
+
+        return one
 
     if args.sweep:
-        key, values = args.sweep.split("=", 1)
+        import itertools
+
+        keys = [sw.split("=", 1)[0] for sw in args.sweep]
+        points = list(itertools.product(*[sw.split("=", 1)[1].split(",") for sw in args.sweep]))
+        shapes = [(args.m, args.k, args.n)] + [tuple(int(x) for x in sh.split(",")) for sh in args.also_shape]
         res = {}
-        for val in values.split(","):
-            capi.set_option(key, int(val))
-            for _ in range(args.warmup):
-                one()
-            t = torch.tensor([one() for _ in range(20)], dtype=torch.float64, device=dev)
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ts = sorted(t.cpu().tolist())
-            code, st = capi.last_status()
-            res[f"{key}={val}"] = {"p50_us": round(ts[10], 2), "min_us": round(ts[0], 2), "max_us": round(ts[-1], 2), "status": code}
-            progress(f"{key}={val}: {res[f'{key}={val}']}")
+        for (m, k, n) in shapes:
+            one = make_step(m, k, n)
+            progress(f"buffers ready for {m}x{k}x{n}")
+            for point in points:
+                for key, val in zip(keys, point):
+                    capi.set_option(key, int(val))
+                for _ in range(args.warmup):
+                    one()
+                t = torch.tensor([one() for _ in range(20)], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ts = sorted(t.cpu().tolist())
+                code, st = capi.last_status()
+                name = f"{m}x{k}x{n} " + " ".join(f"{key}={val}" for key, val in zip(keys, point))
+                res[name] = {"p50_us": round(ts[10], 2), "min_us": round(ts[0], 2), "max_us": round(ts[-1], 2), "status": code}
+                progress(f"{name}: {res[name]}")
         if rank == 0:
-            print(json.dumps({"sweep": res, "world": world, "shape": [args.m, args.k, args.n], "trace_build": capi.TRACE}))
+            print(json.dumps({"sweep": res, "world": world, "trace_build": capi.TRACE}))
         if world > 1:
             dist.barrier()
         capi.finalize()
         if world > 1:
             dist.destroy_process_group()
         return
+    one = make_step(args.m, args.k, args.n)
+    progress("buffers ready")
     for i in range(args.warmup):
         us = one()
         if i == 0:

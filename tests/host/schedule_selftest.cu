@@ -3,7 +3,8 @@
 // at step i (item_coord).  They stand in for the reference's scheduling helpers
 // (include/catccos/catccos.hpp:148-176, include/catccos/dgemm/block/block_swizzle_allgather.hpp:59-90): the
 // contract is "every unit exactly once; this rank's own rows first, then the peers in ring order, slice by
-// slice; inside a send group the K segments in order".  Exit code 0 = pass.
+// slice (or, for a quantiser that sends every item to all ranks at once, slice by slice over all ranks with
+// the own slice leading); inside a send group the K segments in order".  Exit code 0 = pass.
 #include <cstdio>
 #include <set>
 #include <vector>
@@ -20,9 +21,10 @@ using namespace catccos;
         }                                                              \
     } while (0)
 
-static int check_tiles(uint32_t world, uint32_t rank, uint32_t m_local, uint32_t n, bool pair)
+static int check_tiles(uint32_t world, uint32_t rank, uint32_t m_local, uint32_t n, bool pair, bool own_first)
 {
     GemmParams p = {};
+    p.own_first = own_first ? 1u : 0u;
     uint32_t flag_word = 0;
     p.flags = &flag_word;  // gated launch: arrival order
     p.world = world;
@@ -43,7 +45,11 @@ static int check_tiles(uint32_t world, uint32_t rank, uint32_t m_local, uint32_t
             const uint32_t tps = m_local / bm;
             const uint32_t src = t.m_tile / tps, slice = t.m_tile % tps;
             const uint32_t src_pos = (src + world - rank) % world;  // 0 = own shard, 1 = next rank in the ring, ...
-            if (i < tps * n_tiles) {
+            if (!own_first) {
+                // slice by slice over all ranks; inside a slice this rank first, then the ring behind it
+                const uint32_t mo = i / n_tiles;
+                EXPECT(slice == mo / world && src_pos == mo % world);
+            } else if (i < tps * n_tiles) {
                 EXPECT(src == rank);  // this rank's own rows first: they need no transfer
             } else {
                 EXPECT(src != rank);
@@ -93,10 +99,12 @@ int main()
     for (bool pair : {false, true}) {
         for (uint32_t world : {1u, 2u, 4u, 8u}) {
             for (uint32_t rank = 0; rank < world; ++rank) {
-                if (check_tiles(world, rank, 1024, 2304, pair) != 0) return 1;  // the prefill shape
-                if (check_tiles(world, rank, 4096, 3456, pair) != 0) return 1;  // the outlier shape
-                if (check_tiles(world, rank, 16, 4096, pair) != 0) return 1;    // decode: shards smaller than a tile
-                if (check_tiles(world, rank, 190, 272, pair) != 0) return 1;    // ragged
+                for (bool own_first : {true, false}) {
+                    if (check_tiles(world, rank, 1024, 2304, pair, own_first) != 0) return 1;  // the prefill shape
+                    if (check_tiles(world, rank, 4096, 3456, pair, own_first) != 0) return 1;  // the outlier shape
+                    if (check_tiles(world, rank, 16, 4096, pair, own_first) != 0) return 1;    // decode: shards smaller than a tile
+                    if (check_tiles(world, rank, 190, 272, pair, own_first) != 0) return 1;    // ragged
+                }
             }
         }
     }

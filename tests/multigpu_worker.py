@@ -109,6 +109,63 @@ def main():
                 assert torch.equal(c2, c), "pre-quantised and fused paths must agree bit for bit"
         capi.set_option("fuse_mode", -1)
         capi.symm_free(symm)
+    # ---- MXFP8 Matmul + ReduceScatter: rank r keeps row chunk r of the sum of all ranks' products.  Every rank
+    # draws all ranks' operands from one seed, so each can compute the whole golden sum ----
+    for (m, k, n) in [(256, 512, 512), (1024, 1024, 2304)]:
+        t = capi.make_tiling(m, k, n, world)
+        symm = capi.symm_alloc(capi.symm_bytes_needed(t, 2))
+        for rnd in range(3):  # both stages, and the first one again
+            rng = np.random.default_rng(7000 + rnd)
+            gold = np.zeros((m, n), np.float32)
+            mine = None
+            for r in range(world):
+                aq = mx_oracle.quantize_rows(workloads.f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+                bq = mx_oracle.quantize_weight(workloads.f32_to_bf16_bits(rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.05)))
+                gold += mx_oracle.gemm_f32(mx_oracle.dequant_rows(*aq), mx_oracle.dequant_weight(*bq))
+                if r == rank:
+                    mine = [torch.from_numpy(x).cuda() for x in (aq[0], aq[1], bq[0], bq[1])]
+            d = torch.zeros((m // world, n), dtype=torch.bfloat16, device="cuda")
+            torch.distributed.barrier()
+            capi.mxfp8_matmul_reduce_scatter(mine[0], mine[1], mine[2], mine[3], d, symm, world)
+            status_ok(("mmrs", m, rnd))
+            rows = m // world
+            bad, maxdiff = mx_oracle.check_close(d.float().cpu().numpy(), gold[rank * rows:(rank + 1) * rows], 1e-2, 1e-3)
+            assert bad == 0, ("mmrs", m, rnd, rank, bad, maxdiff)
+        torch.distributed.barrier()
+        capi.symm_free(symm)
+
+    # ---- FP4 AllGather-Matmul: packed E2M1 operands, A gathered in packed form ----
+    for (m, k, n) in [(256, 1024, 512)]:
+        t = capi.make_tiling(m, k, n, world)
+        symm = capi.symm_alloc(capi.symm_bytes_needed(t, False))
+        for rnd in range(2):
+            rng = np.random.default_rng(8000 + rnd)
+            aq = [mx_oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+                  for _ in range(world)]
+            a_deq = np.concatenate([mx_oracle.dequant_rows_e2m1(pk, sc) for pk, sc in aq])
+            bw = None
+            for r in range(world):
+                b = rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.05)
+                if r != rank:
+                    continue
+                pt, st = mx_oracle.quantize_rows_e2m1(workloads.f32_to_bf16_bits(np.ascontiguousarray(b.T)))  # [N, K/2], [N, K/32]
+                nib = np.empty((n, k), np.uint8)
+                nib[:, 0::2] = pt & 0x0F
+                nib[:, 1::2] = pt >> 4
+                nib = np.ascontiguousarray(nib.T)  # [K, N] one code per byte, then packed along N
+                bw = ((nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8),
+                      np.ascontiguousarray(st.T.reshape(k // 64, 2, n).transpose(0, 2, 1)),
+                      mx_oracle.dequant_rows_e2m1(pt, st).T.copy())
+            a_p, a_s = torch.from_numpy(aq[rank][0]).cuda(), torch.from_numpy(aq[rank][1]).cuda()
+            b_p, b_s = torch.from_numpy(bw[0]).cuda(), torch.from_numpy(bw[1]).cuda()
+            c = torch.zeros((world * m, n), dtype=torch.bfloat16, device="cuda")
+            torch.distributed.barrier()
+            capi.fp4_mx_allgather_matmul(a_p, a_s, b_p, b_s, c, symm, world)
+            status_ok(("fp4", m, rnd))
+            bad, maxdiff = mx_oracle.check_close(c.float().cpu().numpy(), mx_oracle.gemm_f32(a_deq, bw[2]), 1e-2, 1e-3)
+            assert bad == 0, ("fp4", m, rnd, rank, bad, maxdiff)
+        torch.distributed.barrier()
+        capi.symm_free(symm)
     capi.finalize()
     torch.distributed.destroy_process_group()
     print(f"rank {rank} OK", flush=True)
