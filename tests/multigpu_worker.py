@@ -37,6 +37,9 @@ def main():
     port = int(os.environ.get("MASTER_PORT", "29500")) + 97
     capi.init(rank, world, local, f"tcp://127.0.0.1:{port}")
 
+    # sections to run, e.g. "mmrs,fp4" as the first argument (default: all)
+    only = set(sys.argv[1].split(",")) if len(sys.argv) > 1 else {"quant_ag", "agmm", "mmrs", "fp4"}
+
     def status_ok(tag):
         code, st = capi.last_status()
         assert code == 0, (tag, rank, st)
@@ -45,7 +48,7 @@ def main():
     # ragged M = 8190 at full size (sampled rows), small shapes in full; outputs in plain device memory
     # (through the stage) and in symmetric memory (written by the peers directly) ----
     for (m, k, dist_name) in [(256, 1024, "normal"), (190, 512, "normal"), (4096, 7168, "normal"), (8190, 1024, "normal"),
-                              (512, 5120, "student_t3_outlier")]:
+                              (512, 5120, "student_t3_outlier")] if "quant_ag" in only else []:
         cfg = workloads.Config("q", m, k, 0, (world,), dist_name, "")
         t = capi.make_tiling(m, 1, k, world)
         symm = capi.symm_alloc(capi.symm_bytes_needed(t, True))
@@ -79,7 +82,7 @@ def main():
     # ---- fused allgather-matmul at the benchmark's per-rank sizes: C1, C3, C4, C5; every transfer mode ----
     shapes = [("c1", 256, 1024, 1024, "normal"), ("c3", 1024, 7168, 2304, "normal"),
               ("c4", 4096, 5120, 3456, "student_t3_outlier"), ("c5", 16, 7168, 4096, "normal")]
-    for (name, m, k, n, dist_name) in shapes:
+    for (name, m, k, n, dist_name) in shapes if "agmm" in only else []:
         cfg = workloads.Config(name, m, k, n, (world,), dist_name, "")
         t = capi.make_tiling(m, k, n, world)
         symm = capi.symm_alloc(capi.symm_bytes_needed(t, False))
@@ -111,7 +114,7 @@ def main():
         capi.symm_free(symm)
     # ---- MXFP8 Matmul + ReduceScatter: rank r keeps row chunk r of the sum of all ranks' products.  Every rank
     # draws all ranks' operands from one seed, so each can compute the whole golden sum ----
-    for (m, k, n) in [(256, 512, 512), (1024, 1024, 2304)]:
+    for (m, k, n) in [(256, 512, 512), (1024, 1024, 2304)] if "mmrs" in only else []:
         t = capi.make_tiling(m, k, n, world)
         symm = capi.symm_alloc(capi.symm_bytes_needed(t, 2))
         for rnd in range(3):  # both stages, and the first one again
@@ -135,7 +138,7 @@ def main():
         capi.symm_free(symm)
 
     # ---- FP4 AllGather-Matmul: packed E2M1 operands, A gathered in packed form ----
-    for (m, k, n) in [(256, 1024, 512)]:
+    for (m, k, n) in [(256, 1024, 512)] if "fp4" in only else []:
         t = capi.make_tiling(m, k, n, world)
         symm = capi.symm_alloc(capi.symm_bytes_needed(t, False))
         for rnd in range(2):
