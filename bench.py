@@ -517,10 +517,42 @@ def run_gpu(args) -> None:
             "weight_stream_floor_us": (dcfg.k * dcfg.n_local * 33 / 32) / read_peaks()["hbm_gbs"] / 1e3,
         }
 
+    def fp4_gemm_leg():
+        # the FP4 operator's GEMM (packed E2M1 operands, E8M0 scales per 32 along K) on the headline shape, kernel
+        # alone: the per-call copy of the weight into K-major order and the GEMM.  Random codes; parity of this
+        # path is the tests' business (tests/test_gemm_gpu.py), nothing is checked here.
+        gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+        mg, kk, nn = world * CFG.m_local, CFG.k, CFG.n_local
+        fa = torch.randint(0, 256, (mg, kk // 2), dtype=torch.uint8, device=dev, generator=gen)
+        fas = torch.randint(122, 128, (mg, kk // 32), dtype=torch.uint8, device=dev, generator=gen)
+        fb = torch.randint(0, 256, (kk, nn // 2), dtype=torch.uint8, device=dev, generator=gen)
+        fbs = torch.randint(122, 128, (kk // 64, nn, 2), dtype=torch.uint8, device=dev, generator=gen)
+        capi.set_option("a_dtype", 2)
+        capi.set_option("b_dtype", 2)
+        try:
+            fc = torch.empty((mg, nn), dtype=torch.bfloat16, device=dev)
+            lib, stream = capi.load(), torch.cuda.current_stream().cuda_stream
+
+            def fp4_call():
+                rc = lib.catccos_b200_mx_gemm(stream, fa.data_ptr(), fas.data_ptr(), fb.data_ptr(), fbs.data_ptr(),
+                                              fc.data_ptr(), mg, nn, kk)
+                if rc != 0:
+                    raise RuntimeError(f"catccos_b200_mx_gemm (fp4) returned {rc}")
+
+            f_ms = timed(fp4_call, 20, 3)
+        finally:
+            capi.set_option("a_dtype", 0)
+            capi.set_option("b_dtype", 0)
+        return {"what": f"mx_gemm on packed E2M1 operands [{mg},{kk}] x [{kk},{nn}] (kind::mxf8f6f4: the FP8 issue rate), "
+                        "weight copied to K-major order inside every call",
+                "ms_per_call": float(f_ms.mean()), "ms_stats": stats(f_ms),
+                "tflops_per_gpu": flops_per_gpu / (float(f_ms.mean()) * 1e-3) / 1e12}
+
     if not args.lean:
         leg("quant_allgather", quant_allgather_leg)
         leg("decode_c5", decode_leg)
         leg("unfused_baseline", unfused_leg)
+        leg("fp4_gemm", fp4_gemm_leg)
     code, st = capi.last_status()
     if code != 0:
         raise SystemExit(f"device-side wait ran out in an extra leg: {st}")
