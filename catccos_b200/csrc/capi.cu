@@ -656,7 +656,7 @@ int launch_gemm(RankCtx& rc, cudaStream_t st, const void* a, const void* b, Gemm
             CUDA_TRY(cudaMalloc(&rc.fp4_bt, need));
             rc.fp4_bt_bytes = need;
         }
-        dim3 tg((p.N + 63) / 64, (p.K + 63) / 64);
+        dim3 tg((p.N + kFp4TransN - 1) / kFp4TransN, (p.K + kFp4TransK - 1) / kFp4TransK);
         fp4_transpose_kernel<<<tg, 256, 0, st>>>(static_cast<const uint8_t*>(b), rc.fp4_bt, p.K, p.N);
         g_launches++;
         CUDA_TRY(cudaGetLastError());

@@ -772,28 +772,45 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quant_scatter_packed_kernel(
 
 // Transposed copy of a packed E2M1 weight: in [K, N/2] (two N-neighbours per byte, low nibble = even column, the
 // reference's file layout, examples/utils/gen_data_fp4_mx_allgather_matmul.py:521-544) -> out [N, K/2] (two
-// K-neighbours per byte).  The tensor core reads 4-bit operands K-major only.  64 x 64 values per CTA.
+// K-neighbours per byte).  The tensor core reads 4-bit operands K-major only.  64 (K) x 256 (N) values per CTA,
+// one value per byte in shared memory; global memory is read and written in 32-bit words (a warp reads 128
+// contiguous bytes of a K row, eight lanes write 32 contiguous bytes of an N row).  Needs N % 8 == 0 and
+// K % 64 == 0 (the GEMM asks for N % 16 == 0 and K % 128 == 0) and 4-byte aligned pointers.
+constexpr uint32_t kFp4TransK = 64, kFp4TransN = 256;
 __global__ void __launch_bounds__(256) fp4_transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t K,
                                                             uint32_t N)
 {
-    __shared__ uint8_t tile[64][65];  // one value per byte
-    const uint32_t k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
-        const uint32_t r = i / 32, cb = i % 32;  // row of K, byte of N
-        const uint32_t k = k0 + r, n = n0 + cb * 2;
-        uint8_t b = 0;
+    constexpr uint32_t kStride = kFp4TransN + 4;  // bytes per tile row: rows stay 4-byte aligned, columns shift banks
+    __shared__ __align__(4) uint8_t tile[kFp4TransK * kStride];
+    const uint32_t k0 = blockIdx.y * kFp4TransK, n0 = blockIdx.x * kFp4TransN;
+    const uint32_t in_words = N / 8, out_words = K / 8;  // 32-bit words (eight values) per row
+    const uint32_t* in32 = reinterpret_cast<const uint32_t*>(in);
+    uint32_t* out32 = reinterpret_cast<uint32_t*>(out);
+    for (uint32_t i = threadIdx.x; i < kFp4TransK * (kFp4TransN / 8); i += 256) {
+        const uint32_t r = i / (kFp4TransN / 8), w = i % (kFp4TransN / 8);
+        const uint32_t k = k0 + r, n = n0 + w * 8;
+        uint32_t v = 0;
         if (k < K && n < N) {
-            b = in[(size_t)k * (N / 2) + n / 2];
+            v = __ldg(in32 + (size_t)k * in_words + n / 8);
         }
-        tile[r][cb * 2] = b & 0x0F;
-        tile[r][cb * 2 + 1] = b >> 4;
+        // byte j of v holds columns n + 2j (low nibble) and n + 2j + 1 (high nibble): spread to one value per byte
+        const uint32_t lo = v & 0x0F0F0F0Fu, hi = (v >> 4) & 0x0F0F0F0Fu;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * kStride + w * 8);
+        dst[0] = __byte_perm(lo, hi, 0x5140);  // columns n .. n + 3
+        dst[1] = __byte_perm(lo, hi, 0x7362);  // columns n + 4 .. n + 7
     }
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
-        const uint32_t c = i / 32, kb = i % 32;  // row of N, byte of K
-        const uint32_t n = n0 + c, k = k0 + kb * 2;
+    for (uint32_t i = threadIdx.x; i < kFp4TransN * (kFp4TransK / 8); i += 256) {
+        const uint32_t c = i / (kFp4TransK / 8), kw = i % (kFp4TransK / 8);
+        const uint32_t n = n0 + c, k = k0 + kw * 8;
         if (n < N && k < K) {
-            out[(size_t)n * (K / 2) + k / 2] = (uint8_t)(tile[kb * 2][c] | (tile[kb * 2 + 1][c] << 4));
+            uint32_t word = 0;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t even = tile[(kw * 8 + 2 * j) * kStride + c], odd = tile[(kw * 8 + 2 * j + 1) * kStride + c];
+                word |= (even | (odd << 4)) << (8 * j);
+            }
+            out32[(size_t)n * out_words + k / 8] = word;
         }
     }
 }
